@@ -1,0 +1,499 @@
+// Quantizer kernels: per-tensor absmax, row-wise INT8/E4M3, MX (E8M0 per 32) and NVFP4
+// (E4M3 per 16 + fp32 tensor scale), scale-factor swizzle, block dequantizer.
+//
+// All of them are one-pass, HBM-bound byte producers: 128-bit loads, block maxima in
+// registers (shuffles only where a block spans lanes), 64/128-bit stores.  Results must
+// equal the torch reference bit for bit, which fixes two things:
+//   * quotients are correctly rounded fp32 divisions.  divide_exact() gets them with one
+//     correctly rounded reciprocal per block and two FMA residual corrections per element
+//     (Markstein's theorem: a faithful quotient corrected once with an exactly computed
+//     residual and a correctly rounded reciprocal is the correctly rounded quotient; the
+//     first correction makes the estimate faithful, the second makes it exact);
+//   * narrow formats are produced by the cvt.rn.satfinite instructions, which round to
+//     nearest even exactly like the reference's casts and threshold chains.
+#include <type_traits>
+
+#include "gnk_common.cuh"
+
+namespace gnk {
+namespace {
+
+// x / d for d > 0, given r = __frcp_rn(d).  Correctly rounded when the quotient is far
+// from overflow and x is not within 2^-100 of zero (then the result only feeds a
+// rounding to zero); `safe` = false takes the plain IEEE division instead.
+__device__ __forceinline__ float divide_exact(float x, float d, float r, bool safe) {
+  if (!safe) return __fdiv_rn(x, d);
+  float q = __fmul_rn(x, r);
+  float e = __fmaf_rn(-d, q, x);
+  q = __fmaf_rn(e, r, q);
+  e = __fmaf_rn(-d, q, x);
+  q = __fmaf_rn(e, r, q);
+  return copysignf(q, x);  // x = -0 must stay -0 (the packers copy the sign bit)
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {  // low byte <- lo
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// 8 floats -> 8 E2M1 codes in 4 bytes; element 2i goes to the HIGH nibble of byte i.
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&v)[8]) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %1, %2;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %3, %4;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %5, %6;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %7, %8;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return r;
+}
+__device__ __forceinline__ float e4m3_to_f32(uint32_t code) {
+  uint32_t h2;
+  uint16_t c = static_cast<uint16_t>(code & 0xFF);
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(c));
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xFFFF)));
+}
+__device__ __forceinline__ float e5m2_to_f32(uint32_t code) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>((code & 0xFF) << 8)));
+}
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+  const float mag = (code & 4) ? ((code & 2) ? ((code & 1) ? 6.f : 4.f) : ((code & 1) ? 3.f : 2.f))
+                               : ((code & 2) ? ((code & 1) ? 1.5f : 1.f) : ((code & 1) ? .5f : 0.f));
+  return (code & 8) ? -mag : mag;
+}
+
+__device__ __forceinline__ float amax8(const float (&v)[8]) {
+  float m = fabsf(v[0]);
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+__device__ __forceinline__ size_t sf_offset(int64_t row, int64_t kcol, int64_t ks_padded, bool swizzled,
+                                            int64_t ks) {
+  if (!swizzled) return static_cast<size_t>(row * ks + kcol);
+  const int64_t mb = row >> 7, r = row & 127;
+  return static_cast<size_t>(((mb * (ks_padded >> 2) + (kcol >> 2)) * 32 + (r & 31)) * 16 + (r >> 5) * 4 + (kcol & 3));
+}
+
+// ------------------------------------------------------------------------------------
+// per-tensor absmax: partial maxima per CTA in scratch, last CTA (ticket) folds them
+// ------------------------------------------------------------------------------------
+constexpr int kAbsmaxMaxCtas = 2048;
+constexpr int kAbsmaxThreads = 256;
+
+template <typename T>
+__device__ __forceinline__ float absmax_partial(const T* __restrict__ x, int64_t n) {
+  float m = 0.f;
+  const int64_t nvec = n >> 3;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    load8<T>(x + i * 8, v);
+    m = fmaxf(m, amax8(v));
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) m = fmaxf(m, fabsf(to_f32<T>(x[(nvec << 3) + threadIdx.x])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  return m;
+}
+
+// scratch[0] = ticket (zero on entry, zero again on exit), scratch[1 + cta] = partial maxima
+template <typename T>
+__global__ void __launch_bounds__(kAbsmaxThreads) absmax_kernel(const T* __restrict__ x, int64_t n,
+                                                                float* __restrict__ out,
+                                                                unsigned int* __restrict__ scratch) {
+  __shared__ float warp_max[kAbsmaxThreads / 32];
+  __shared__ bool is_last;
+  float m = absmax_partial<T>(x, n);
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float b = warp_max[0];
+    for (int i = 1; i < kAbsmaxThreads / 32; ++i) b = fmaxf(b, warp_max[i]);
+    reinterpret_cast<float*>(scratch)[1 + blockIdx.x] = b;
+    __threadfence();
+    is_last = atomicAdd(&scratch[0], 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float f = 0.f;
+  for (int i = threadIdx.x; i < gridDim.x; i += blockDim.x)
+    f = fmaxf(f, reinterpret_cast<volatile float*>(scratch)[1 + i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, o));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = f;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float b = warp_max[0];
+    for (int i = 1; i < kAbsmaxThreads / 32; ++i) b = fmaxf(b, warp_max[i]);
+    out[0] = b;
+    scratch[0] = 0u;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// row-wise quantizer: LPR lanes share a row; pass 1 amax, pass 2 (row now in L1/L2) encode
+// ------------------------------------------------------------------------------------
+template <typename T, int QKIND, int LPR>
+__global__ void __launch_bounds__(256) quant_rowwise_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
+                                                            int64_t ldx, uint8_t* __restrict__ q,
+                                                            float* __restrict__ scale, int64_t perm_h,
+                                                            int64_t perm_l) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % LPR;
+  const int64_t rows_per_cta = (256 / LPR);
+  const int64_t row = blockIdx.x * rows_per_cta + threadIdx.x / LPR;
+  const bool live = row < rows;
+  const T* xr = x + (live ? row : 0) * ldx;
+
+  float m = 0.f;
+  if (live)
+    for (int64_t c = sub * 8; c < cols; c += LPR * 8) {
+      float v[8];
+      load8<T>(xr + c, v);
+      m = fmaxf(m, amax8(v));
+    }
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (!live) return;
+
+  const float qmax = QKIND == GNK_Q_INT8 ? 127.f : 448.f;
+  const float s = __fdiv_rn(m, qmax);
+  const float d = fmaxf(s, 1e-6f);
+  const float r = __frcp_rn(d);
+  const bool safe = m >= 1e-30f;  // quotients are <= qmax * (1 + eps) then; tiny rows take the slow path
+  if (sub == 0) {
+    int64_t idx = row;
+    if (perm_h > 0) {
+      const int64_t h = row % perm_h, bl = row / perm_h, l = bl % perm_l, b = bl / perm_l;
+      idx = (b * perm_h + h) * perm_l + l;
+    }
+    scale[idx] = s;
+  }
+  uint8_t* qr = q + row * cols;
+  for (int64_t c = sub * 8; c < cols; c += LPR * 8) {
+    float v[8];
+    load8<T>(xr + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = divide_exact(v[i], d, r, safe);
+    uint2 out;
+    if constexpr (QKIND == GNK_Q_INT8) {
+      uint32_t b[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = fminf(fmaxf(rintf(v[i]), -128.f), 127.f);
+        b[i] = static_cast<uint32_t>(static_cast<int>(t)) & 0xFFu;
+      }
+      out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+      out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+    } else {
+      out.x = cvt_e4m3x2(v[0], v[1]) | (cvt_e4m3x2(v[2], v[3]) << 16);
+      out.y = cvt_e4m3x2(v[4], v[5]) | (cvt_e4m3x2(v[6], v[7]) << 16);
+    }
+    *reinterpret_cast<uint2*>(qr + c) = out;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// MX quantizer: one thread per 32-element block
+// ------------------------------------------------------------------------------------
+template <typename T, int QKIND, int RULE>
+__global__ void __launch_bounds__(256) quant_mx_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
+                                                       uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                       int swizzled, int64_t rows_out, int64_t ks_out) {
+  const int64_t ks = K >> 5;
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= rows_out * ks_out) return;
+  const int64_t row = idx / ks_out, kb = idx % ks_out;
+  if (row >= M || kb >= ks) {  // padding of the swizzled layout
+    sf[sf_offset(row, kb, ks_out, true, ks)] = 0;
+    return;
+  }
+  const T* p = x + row * ldx + kb * 32;
+  float v[4][8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) load8<T>(p + j * 8, v[j]);
+  float m = fmaxf(fmaxf(amax8(v[0]), amax8(v[1])), fmaxf(amax8(v[2]), amax8(v[3])));
+
+  constexpr float kPow2 = QKIND == GNK_Q_E4M3 ? 256.f : QKIND == GNK_Q_E5M2 ? 32768.f : 4.f;
+  constexpr float kAmax = QKIND == GNK_Q_E4M3 ? 448.f : QKIND == GNK_Q_E5M2 ? 57344.f : 6.f;
+  uint32_t ebits;
+  if constexpr (RULE == GNK_MX_OCP) {
+    const float p2 = __uint_as_float(__float_as_uint(m) & 0x7F800000u);
+    ebits = __float_as_uint(__fdiv_rn(p2, kPow2)) >> 23;
+  } else {
+    const uint32_t b = __float_as_uint(__fdiv_rn(m, kAmax));
+    const uint32_t e = b >> 23, man = b & 0x7FFFFFu;
+    const bool bump = (e > 0 && e < 254 && man > 0) || (e == 0 && man > 0x400000u);
+    ebits = bump ? e + 1 : e;
+  }
+  sf[sf_offset(row, kb, ks_out, swizzled != 0, ks)] = static_cast<uint8_t>(ebits);
+
+  const float denom = __uint_as_float(ebits << 23);
+  const bool clipped = !(denom >= 1e-12f);
+  // 1 / 2^(e-127) is exact (a subnormal for e = 254), so the product equals the quotient
+  const float recip = __uint_as_float(ebits >= 254 ? 0x00400000u : (254u - ebits) << 23);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float y = clipped ? __fdiv_rn(v[j][i], 1e-12f) : __fmul_rn(v[j][i], recip);
+      v[j][i] = fminf(fmaxf(y, -kAmax), kAmax);
+    }
+  if constexpr (QKIND == GNK_Q_E2M1) {
+    uint4 out = make_uint4(cvt_e2m1x8(v[0]), cvt_e2m1x8(v[1]), cvt_e2m1x8(v[2]), cvt_e2m1x8(v[3]));
+    *reinterpret_cast<uint4*>(q + row * (K >> 1) + kb * 16) = out;
+  } else {
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if constexpr (QKIND == GNK_Q_E4M3) {
+        w[2 * j] = cvt_e4m3x2(v[j][0], v[j][1]) | (cvt_e4m3x2(v[j][2], v[j][3]) << 16);
+        w[2 * j + 1] = cvt_e4m3x2(v[j][4], v[j][5]) | (cvt_e4m3x2(v[j][6], v[j][7]) << 16);
+      } else {
+        w[2 * j] = cvt_e5m2x2(v[j][0], v[j][1]) | (cvt_e5m2x2(v[j][2], v[j][3]) << 16);
+        w[2 * j + 1] = cvt_e5m2x2(v[j][4], v[j][5]) | (cvt_e5m2x2(v[j][6], v[j][7]) << 16);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(q + row * K + kb * 32);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// NVFP4 quantizer: one thread per 16-element block
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) quant_nvfp4_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
+                                                          const float* __restrict__ tensor_scale, float eps,
+                                                          uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                          int swizzled, int64_t rows_out, int64_t ks_out) {
+  const int64_t ks = K >> 4;
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= rows_out * ks_out) return;
+  const int64_t row = idx / ks_out, kb = idx % ks_out;
+  if (row >= M || kb >= ks) {
+    sf[sf_offset(row, kb, ks_out, true, ks)] = 0;
+    return;
+  }
+  const T* p = x + row * ldx + kb * 16;
+  float v[2][8];
+  load8<T>(p, v[0]);
+  load8<T>(p + 8, v[1]);
+  const float m = fmaxf(amax8(v[0]), amax8(v[1]));
+  const float ts = __ldg(tensor_scale);
+
+  const float d0 = fmaxf(__fmul_rn(6.f, ts), 1e-12f);
+  const float s32 = fminf(__fdiv_rn(m, d0), 448.f);
+  const uint32_t code = cvt_e4m3x2(s32, 0.f) & 0xFFu;
+  sf[sf_offset(row, kb, ks_out, swizzled != 0, ks)] = static_cast<uint8_t>(code);
+
+  const float d1 = fmaxf(__fmul_rn(ts, e4m3_to_f32(code)), eps);
+  const float r = __frcp_rn(d1);
+  // |x| <= m, so every quotient is below m * r * (1 + 2^-22); keep far from overflow, and
+  // keep d1 / r in the normal range so the residuals are exact
+  const bool safe = (m * r < 1e30f) && (d1 > 1e-30f) && (d1 < 1e30f);
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[j][i] = divide_exact(v[j][i], d1, r, safe);
+  uint2 out = make_uint2(cvt_e2m1x8(v[0]), cvt_e2m1x8(v[1]));
+  *reinterpret_cast<uint2*>(q + row * (K >> 1) + kb * 8) = out;
+}
+
+// ------------------------------------------------------------------------------------
+// scale-factor swizzle / unswizzle, block dequantizer
+// ------------------------------------------------------------------------------------
+__global__ void sf_swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t M, int64_t Ks,
+                                  int64_t Mp, int64_t Kp, int to_swizzled) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= Mp * Kp) return;
+  const int64_t row = i / Kp, kc = i % Kp;
+  const size_t sw = sf_offset(row, kc, Kp, true, Kp);
+  if (to_swizzled)
+    dst[sw] = (row < M && kc < Ks) ? src[row * Ks + kc] : 0;
+  else
+    dst[i] = src[sw];
+}
+
+__global__ void dequant_block_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf, int64_t M,
+                                     int64_t K, int qkind, int block, const float* __restrict__ tensor_scale,
+                                     float* __restrict__ out) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= M * K) return;
+  const int64_t row = i / K, c = i % K;
+  float v;
+  if (qkind == GNK_Q_E2M1) {
+    const uint32_t byte = q[row * (K >> 1) + (c >> 1)];
+    v = e2m1_to_f32((c & 1) ? (byte & 0xF) : (byte >> 4));
+  } else if (qkind == GNK_Q_E4M3) {
+    v = e4m3_to_f32(q[i]);
+  } else {
+    v = e5m2_to_f32(q[i]);
+  }
+  const uint32_t s = sf[row * (K / block) + c / block];
+  float sv = block == 32 ? __uint_as_float(s << 23) : e4m3_to_f32(s);
+  if (tensor_scale) sv = __fmul_rn(sv, __ldg(tensor_scale));
+  out[i] = __fmul_rn(v, sv);
+}
+
+template <typename F>
+int dispatch_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case GNK_BF16: return f(static_cast<const __nv_bfloat16*>(nullptr));
+    case GNK_F16: return f(static_cast<const __half*>(nullptr));
+    case GNK_F32: return f(static_cast<const float*>(nullptr));
+    default: return GNK_ERR_BAD_ARG;
+  }
+}
+
+}  // namespace
+}  // namespace gnk
+
+using namespace gnk;
+
+extern "C" size_t gnk_absmax_scratch_bytes(int64_t) { return sizeof(unsigned int) * (1 + kAbsmaxMaxCtas); }
+
+extern "C" int gnk_absmax(const void* x, int dtype, int64_t n, float* out, void* scratch, gnk_stream_t stream) {
+  if (!x || !out || !scratch || n <= 0) return GNK_ERR_BAD_ARG;
+  if (!aligned16(x)) return GNK_ERR_BAD_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int64_t want = (n / 8 + kAbsmaxThreads - 1) / kAbsmaxThreads;
+  int grid = static_cast<int>(want < 1 ? 1 : (want > kAbsmaxMaxCtas ? kAbsmaxMaxCtas : want));
+  int cap = num_sms() * 8;
+  if (grid > cap) grid = cap;
+  if (grid > kAbsmaxMaxCtas) grid = kAbsmaxMaxCtas;
+  return dispatch_dtype(dtype, [&](auto* tag) -> int {
+    using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+    absmax_kernel<T><<<grid, kAbsmaxThreads, 0, st>>>(static_cast<const T*>(x), n, out,
+                                                       static_cast<unsigned int*>(scratch));
+    GNK_LAUNCH_OK();
+    return (int)GNK_OK;
+  });
+}
+
+template <typename T, int QKIND>
+static int launch_rowwise(const T* x, int64_t rows, int64_t cols, int64_t ldx, uint8_t* q, float* scale,
+                          int64_t perm_h, int64_t perm_l, cudaStream_t st) {
+  int lpr = 32;
+  while (lpr > 1 && (lpr / 2) * 8 >= cols) lpr /= 2;
+  const int64_t rows_per_cta = 256 / lpr;
+  const unsigned grid = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta);
+#define GNK_RW(L)                                                                                          \
+  case L:                                                                                                  \
+    quant_rowwise_kernel<T, QKIND, L><<<grid, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); \
+    break;
+  switch (lpr) {
+    GNK_RW(1) GNK_RW(2) GNK_RW(4) GNK_RW(8) GNK_RW(16) GNK_RW(32)
+  }
+#undef GNK_RW
+  GNK_LAUNCH_OK();
+  return GNK_OK;
+}
+
+extern "C" int gnk_quant_rowwise(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int qkind,
+                                 void* q, float* scale, int64_t perm_h, int64_t perm_l, gnk_stream_t stream) {
+  if (!x || !q || !scale || rows <= 0 || cols <= 0) return GNK_ERR_BAD_ARG;
+  if (qkind != GNK_Q_INT8 && qkind != GNK_Q_E4M3) return GNK_ERR_BAD_ARG;
+  if (cols % 8 != 0 || ldx % 8 != 0) return GNK_ERR_BAD_SHAPE;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7)) return GNK_ERR_BAD_ALIGN;
+  if (perm_h > 0 && (perm_l <= 0 || rows % (perm_h * perm_l) != 0)) return GNK_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dispatch_dtype(dtype, [&](auto* tag) -> int {
+    using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+    if (qkind == GNK_Q_INT8)
+      return launch_rowwise<T, GNK_Q_INT8>(static_cast<const T*>(x), rows, cols, ldx, static_cast<uint8_t*>(q), scale,
+                                           perm_h, perm_l, st);
+    return launch_rowwise<T, GNK_Q_E4M3>(static_cast<const T*>(x), rows, cols, ldx, static_cast<uint8_t*>(q), scale,
+                                         perm_h, perm_l, st);
+  });
+}
+
+extern "C" int gnk_quant_mx(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int qkind, int rule, void* q,
+                            uint8_t* sf, int sf_swizzled, gnk_stream_t stream) {
+  if (!x || !q || !sf || M <= 0 || K <= 0) return GNK_ERR_BAD_ARG;
+  if (qkind != GNK_Q_E4M3 && qkind != GNK_Q_E5M2 && qkind != GNK_Q_E2M1) return GNK_ERR_BAD_ARG;
+  if (rule != GNK_MX_OCP && rule != GNK_MX_NV) return GNK_ERR_BAD_ARG;
+  if (K % 32 != 0 || ldx % 8 != 0) return GNK_ERR_BAD_SHAPE;
+  if (!aligned16(x) || !aligned16(q)) return GNK_ERR_BAD_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t ks = K / 32;
+  const int64_t rows_out = sf_swizzled ? (M + 127) / 128 * 128 : M;
+  const int64_t ks_out = sf_swizzled ? (ks + 3) / 4 * 4 : ks;
+  const int64_t nblk = (rows_out * ks_out + 255) / 256;
+  if (nblk > 0x7FFFFFFF) return GNK_ERR_TOO_LARGE;
+  const unsigned grid = static_cast<unsigned>(nblk);
+  return dispatch_dtype(dtype, [&](auto* tag) -> int {
+    using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+    const T* xp = static_cast<const T*>(x);
+    uint8_t* qp = static_cast<uint8_t*>(q);
+#define GNK_MXK(QK, RL) quant_mx_kernel<T, QK, RL><<<grid, 256, 0, st>>>(xp, M, K, ldx, qp, sf, sf_swizzled, rows_out, ks_out)
+    if (rule == GNK_MX_OCP) {
+      if (qkind == GNK_Q_E4M3) GNK_MXK(GNK_Q_E4M3, GNK_MX_OCP);
+      else if (qkind == GNK_Q_E5M2) GNK_MXK(GNK_Q_E5M2, GNK_MX_OCP);
+      else GNK_MXK(GNK_Q_E2M1, GNK_MX_OCP);
+    } else {
+      if (qkind == GNK_Q_E4M3) GNK_MXK(GNK_Q_E4M3, GNK_MX_NV);
+      else if (qkind == GNK_Q_E5M2) GNK_MXK(GNK_Q_E5M2, GNK_MX_NV);
+      else GNK_MXK(GNK_Q_E2M1, GNK_MX_NV);
+    }
+#undef GNK_MXK
+    GNK_LAUNCH_OK();
+    return (int)GNK_OK;
+  });
+}
+
+extern "C" int gnk_quant_nvfp4(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                               const float* tensor_scale, float eps, void* q, uint8_t* sf, int sf_swizzled,
+                               gnk_stream_t stream) {
+  if (!x || !q || !sf || !tensor_scale || M <= 0 || K <= 0) return GNK_ERR_BAD_ARG;
+  if (K % 16 != 0 || ldx % 8 != 0) return GNK_ERR_BAD_SHAPE;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7)) return GNK_ERR_BAD_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t ks = K / 16;
+  const int64_t rows_out = sf_swizzled ? (M + 127) / 128 * 128 : M;
+  const int64_t ks_out = sf_swizzled ? (ks + 3) / 4 * 4 : ks;
+  const int64_t nblk = (rows_out * ks_out + 255) / 256;
+  if (nblk > 0x7FFFFFFF) return GNK_ERR_TOO_LARGE;
+  const unsigned grid = static_cast<unsigned>(nblk);
+  return dispatch_dtype(dtype, [&](auto* tag) -> int {
+    using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+    quant_nvfp4_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), M, K, ldx, tensor_scale, eps,
+                                                 static_cast<uint8_t*>(q), sf, sf_swizzled, rows_out, ks_out);
+    GNK_LAUNCH_OK();
+    return (int)GNK_OK;
+  });
+}
+
+extern "C" int gnk_sf_swizzle(const uint8_t* src, uint8_t* dst, int64_t M, int64_t Ks, int to_swizzled,
+                              gnk_stream_t stream) {
+  if (!src || !dst || M <= 0 || Ks <= 0) return GNK_ERR_BAD_ARG;
+  const int64_t Mp = (M + 127) / 128 * 128, Kp = (Ks + 3) / 4 * 4;
+  if (!to_swizzled && (M != Mp || Ks != Kp)) return GNK_ERR_BAD_SHAPE;
+  const int64_t n = Mp * Kp;
+  sf_swizzle_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, dst, M, Ks, Mp, Kp, to_swizzled);
+  GNK_LAUNCH_OK();
+  return GNK_OK;
+}
+
+extern "C" int gnk_dequant_block(const void* q, const uint8_t* sf, int64_t M, int64_t K, int qkind, int block,
+                                 const float* tensor_scale, float* out, gnk_stream_t stream) {
+  if (!q || !sf || !out || M <= 0 || K <= 0) return GNK_ERR_BAD_ARG;
+  if ((block != 16 && block != 32) || K % block != 0) return GNK_ERR_BAD_SHAPE;
+  if (qkind != GNK_Q_E4M3 && qkind != GNK_Q_E5M2 && qkind != GNK_Q_E2M1) return GNK_ERR_BAD_ARG;
+  const int64_t n = M * K;
+  dequant_block_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(q), sf, M, K, qkind, block, tensor_scale, out);
+  GNK_LAUNCH_OK();
+  return GNK_OK;
+}

@@ -1,0 +1,309 @@
+"""torch custom ops (namespace `gnk::`) over the C ABI of libgnk.so.
+
+Each op allocates its outputs with torch (so the caching allocator and stream semantics
+hold), passes raw device pointers and the current CUDA stream to the library, and raises
+on a non-zero status.  Fake (meta) implementations give shapes and dtypes for tracing.
+Tensors must live on a CUDA device; there is no CPU path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import check, lib
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+_QK = {
+    torch.int8: _lib.Q_INT8,
+    torch.float8_e4m3fn: _lib.Q_E4M3,
+    torch.float8_e5m2: _lib.Q_E5M2,
+    torch.float4_e2m1fn_x2: _lib.Q_E2M1,
+}
+_QK_INV = {v: k for k, v in _QK.items()}
+
+
+def _p(t: Tensor | None):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(t: Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _need_cuda(*ts: Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("gn_kernels_b200 ops need CUDA tensors (there is no CPU implementation)")
+
+
+def _ceil(a: int, b: int) -> int:
+    return -(-a // b) * b
+
+
+# ------------------------------------------------------------------ quantizers
+@torch.library.custom_op("gnk::absmax", mutates_args=())
+def absmax(x: Tensor) -> Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.empty((), dtype=torch.float32, device=x.device)
+    scratch = torch.zeros(lib().gnk_absmax_scratch_bytes(x.numel()) // 4, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().gnk_absmax(_p(x), _DT[x.dtype], x.numel(), _p(out), _p(scratch), _stream(x)), "gnk_absmax")
+    return out
+
+
+@absmax.register_fake
+def _(x):
+    return x.new_empty((), dtype=torch.float32)
+
+
+@torch.library.custom_op("gnk::quant_rowwise", mutates_args=())
+def quant_rowwise(x: Tensor, qkind: int, perm_h: int, perm_l: int) -> tuple[Tensor, Tensor]:
+    """x [..., cols] -> (codes [..., cols] int8/e4m3, scale fp32 [rows] in (optionally permuted) row order)."""
+    _need_cuda(x)
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 != 0:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    q = torch.empty(x.shape, dtype=_QK_INV[qkind], device=x.device)
+    s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib().gnk_quant_rowwise(_p(x2), _DT[x.dtype], rows, cols, x2.stride(0), qkind, _p(q), _p(s), perm_h, perm_l, _stream(x)),
+            "gnk_quant_rowwise",
+        )
+    return q, s
+
+
+@quant_rowwise.register_fake
+def _(x, qkind, perm_h, perm_l):
+    return x.new_empty(x.shape, dtype=_QK_INV[qkind]), x.new_empty(x.numel() // x.shape[-1], dtype=torch.float32)
+
+
+@torch.library.custom_op("gnk::quant_mx", mutates_args=())
+def quant_mx(x: Tensor, qkind: int, rule: int, swizzled: bool) -> tuple[Tensor, Tensor]:
+    _need_cuda(x)
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 != 0:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    qcols = K // 2 if qkind == _lib.Q_E2M1 else K
+    q = torch.empty((*x.shape[:-1], qcols), dtype=_QK_INV[qkind], device=x.device)
+    if swizzled:
+        sf = torch.empty((_ceil(M, 128), _ceil(K // 32, 4)), dtype=torch.float8_e8m0fnu, device=x.device)
+    else:
+        sf = torch.empty((*x.shape[:-1], K // 32), dtype=torch.float8_e8m0fnu, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib().gnk_quant_mx(_p(x2), _DT[x.dtype], M, K, x2.stride(0), qkind, rule, _p(q), _p(sf), int(swizzled), _stream(x)),
+            "gnk_quant_mx",
+        )
+    return q, sf
+
+
+@quant_mx.register_fake
+def _(x, qkind, rule, swizzled):
+    K = x.shape[-1]
+    M = x.numel() // K
+    qcols = K // 2 if qkind == _lib.Q_E2M1 else K
+    q = x.new_empty((*x.shape[:-1], qcols), dtype=_QK_INV[qkind])
+    shape = (_ceil(M, 128), _ceil(K // 32, 4)) if swizzled else (*x.shape[:-1], K // 32)
+    return q, x.new_empty(shape, dtype=torch.float8_e8m0fnu)
+
+
+@torch.library.custom_op("gnk::quant_nvfp4", mutates_args=())
+def quant_nvfp4(x: Tensor, tensor_scale: Tensor, eps: float, swizzled: bool) -> tuple[Tensor, Tensor]:
+    _need_cuda(x, tensor_scale)
+    M, K = x.shape
+    if x.stride(-1) != 1 or (x.stride(0) * x.element_size()) % 16 != 0:
+        x = x.contiguous()
+    ts = tensor_scale.to(torch.float32).reshape(1).contiguous()
+    q = torch.empty((M, K // 2), dtype=torch.float4_e2m1fn_x2, device=x.device)
+    shape = (_ceil(M, 128), _ceil(K // 16, 4)) if swizzled else (M, K // 16)
+    sf = torch.empty(shape, dtype=torch.float8_e4m3fn, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib().gnk_quant_nvfp4(_p(x), _DT[x.dtype], M, K, x.stride(0), _p(ts), eps, _p(q), _p(sf), int(swizzled), _stream(x)),
+            "gnk_quant_nvfp4",
+        )
+    return q, sf
+
+
+@quant_nvfp4.register_fake
+def _(x, tensor_scale, eps, swizzled):
+    M, K = x.shape
+    shape = (_ceil(M, 128), _ceil(K // 16, 4)) if swizzled else (M, K // 16)
+    return x.new_empty((M, K // 2), dtype=torch.float4_e2m1fn_x2), x.new_empty(shape, dtype=torch.float8_e4m3fn)
+
+
+@torch.library.custom_op("gnk::sf_swizzle", mutates_args=())
+def sf_swizzle(sf: Tensor, to_swizzled: bool) -> Tensor:
+    _need_cuda(sf)
+    M, Ks = sf.shape
+    sf = sf.contiguous()
+    out = torch.empty((_ceil(M, 128), _ceil(Ks, 4)), dtype=sf.dtype, device=sf.device)
+    with torch.cuda.device(sf.device):
+        check(lib().gnk_sf_swizzle(_p(sf), _p(out), M, Ks, int(to_swizzled), _stream(sf)), "gnk_sf_swizzle")
+    return out
+
+
+@sf_swizzle.register_fake
+def _(sf, to_swizzled):
+    M, Ks = sf.shape
+    return sf.new_empty((_ceil(M, 128), _ceil(Ks, 4)))
+
+
+@torch.library.custom_op("gnk::dequant_block", mutates_args=())
+def dequant_block(q: Tensor, sf: Tensor, block: int, tensor_scale: Tensor | None) -> Tensor:
+    _need_cuda(q, sf)
+    qkind = _QK[q.dtype]
+    K = q.shape[-1] * (2 if qkind == _lib.Q_E2M1 else 1)
+    M = q.numel() // q.shape[-1]
+    q = q.contiguous()
+    sf = sf.contiguous()
+    out = torch.empty((*q.shape[:-1], K), dtype=torch.float32, device=q.device)
+    ts = tensor_scale.to(torch.float32).reshape(1).contiguous() if tensor_scale is not None else None
+    with torch.cuda.device(q.device):
+        check(lib().gnk_dequant_block(_p(q), _p(sf), M, K, qkind, block, _p(ts), _p(out), _stream(q)), "gnk_dequant_block")
+    return out
+
+
+@dequant_block.register_fake
+def _(q, sf, block, tensor_scale):
+    K = q.shape[-1] * (2 if q.dtype == torch.float4_e2m1fn_x2 else 1)
+    return q.new_empty((*q.shape[:-1], K), dtype=torch.float32)
+
+
+# ------------------------------------------------------------------ matmuls
+def _k_major(t: Tensor, align_bytes: int = 16) -> Tensor:
+    """Returns t ([rows, K]) with K contiguous and a 16-byte aligned row pitch, copying if needed."""
+    if t.stride(-1) == 1 and (t.stride(0) * t.element_size()) % align_bytes == 0 and t.data_ptr() % 16 == 0:
+        return t
+    K = t.shape[1]
+    per = align_bytes // t.element_size()
+    Kp = _ceil(K, per)
+    if Kp == K:
+        return t.contiguous()
+    buf = torch.zeros((t.shape[0], Kp), dtype=torch.uint8 if t.element_size() == 1 else t.dtype, device=t.device)
+    buf = buf.view(t.dtype) if t.element_size() == 1 else buf
+    buf[:, :K] = t
+    return buf[:, :K]
+
+
+@torch.library.custom_op("gnk::mm_bf16", mutates_args=())
+def mm_bf16(A: Tensor, Bt: Tensor) -> Tensor:
+    _need_cuda(A, Bt)
+    M, K = A.shape
+    N = Bt.shape[0]
+    A, Bt = _k_major(A), _k_major(Bt)
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    with torch.cuda.device(A.device):
+        check(lib().gnk_mm_bf16(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(C), N, M, N, K, _stream(A)), "gnk_mm_bf16")
+    return C
+
+
+@mm_bf16.register_fake
+def _(A, Bt):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("gnk::mm_i8", mutates_args=())
+def mm_i8(A: Tensor, Bt: Tensor, scale_A: Tensor | None, scale_B: Tensor | None, bias: Tensor | None, out_i32: bool) -> Tensor:
+    _need_cuda(A, Bt)
+    M, K = A.shape
+    N = Bt.shape[0]
+    A, Bt = _k_major(A), _k_major(Bt)
+    C = torch.empty((M, N), dtype=torch.int32 if out_i32 else torch.bfloat16, device=A.device)
+    f = lambda t: t.to(torch.float32).contiguous() if t is not None else None  # noqa: E731
+    sa, sb, bi = f(scale_A), f(scale_B), f(bias)
+    with torch.cuda.device(A.device):
+        check(
+            lib().gnk_mm_i8(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(C), N, M, N, K, _p(sa), _p(sb), _p(bi),
+                            _lib.OUT_I32 if out_i32 else _lib.OUT_BF16, _stream(A)),
+            "gnk_mm_i8",
+        )
+    return C
+
+
+@mm_i8.register_fake
+def _(A, Bt, scale_A, scale_B, bias, out_i32):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.int32 if out_i32 else torch.bfloat16)
+
+
+@torch.library.custom_op("gnk::mm_f8", mutates_args=())
+def mm_f8(A: Tensor, Bt: Tensor, scale_A: Tensor | None, scale_B: Tensor | None, bias: Tensor | None) -> Tensor:
+    _need_cuda(A, Bt)
+    M, K = A.shape
+    N = Bt.shape[0]
+    A, Bt = _k_major(A), _k_major(Bt)
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    f = lambda t: t.to(torch.float32).contiguous() if t is not None else None  # noqa: E731
+    sa, sb, bi = f(scale_A), f(scale_B), f(bias)
+    with torch.cuda.device(A.device):
+        check(
+            lib().gnk_mm_f8(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(C), N, M, N, K, _p(sa), _p(sb), _p(bi), _stream(A)),
+            "gnk_mm_f8",
+        )
+    return C
+
+
+@mm_f8.register_fake
+def _(A, Bt, scale_A, scale_B, bias):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("gnk::mm_mxfp8", mutates_args=())
+def mm_mxfp8(A: Tensor, Bt: Tensor, SFA: Tensor, SFB: Tensor) -> Tensor:
+    _need_cuda(A, Bt, SFA, SFB)
+    M, K = A.shape
+    N = Bt.shape[0]
+    A, Bt = _k_major(A), _k_major(Bt)
+    SFA, SFB = SFA.contiguous(), SFB.contiguous()
+    need_a = _ceil(M, 128) * _ceil(K // 32, 4)
+    need_b = _ceil(N, 128) * _ceil(K // 32, 4)
+    if SFA.numel() < need_a or SFB.numel() < need_b:
+        raise ValueError(f"swizzled scale buffers too small: need {need_a} / {need_b} bytes, got {SFA.numel()} / {SFB.numel()}")
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    with torch.cuda.device(A.device):
+        check(
+            lib().gnk_mm_mxfp8(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(SFA), _p(SFB), _p(C), N, M, N, K, _stream(A)),
+            "gnk_mm_mxfp8",
+        )
+    return C
+
+
+@mm_mxfp8.register_fake
+def _(A, Bt, SFA, SFB):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("gnk::mm_nvfp4", mutates_args=())
+def mm_nvfp4(A: Tensor, Bt: Tensor, SFA: Tensor, SFB: Tensor, alpha: float) -> Tensor:
+    _need_cuda(A, Bt, SFA, SFB)
+    M, Kh = A.shape
+    K = Kh * 2
+    N = Bt.shape[0]
+    A, Bt = _k_major(A), _k_major(Bt)
+    SFA, SFB = SFA.contiguous(), SFB.contiguous()
+    need_a = _ceil(M, 128) * _ceil(K // 16, 4)
+    need_b = _ceil(N, 128) * _ceil(K // 16, 4)
+    if SFA.numel() < need_a or SFB.numel() < need_b:
+        raise ValueError(f"swizzled scale buffers too small: need {need_a} / {need_b} bytes, got {SFA.numel()} / {SFB.numel()}")
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    with torch.cuda.device(A.device):
+        check(
+            lib().gnk_mm_nvfp4(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(SFA), _p(SFB), float(alpha), _p(C), N, M, N, K, _stream(A)),
+            "gnk_mm_nvfp4",
+        )
+    return C
+
+
+@mm_nvfp4.register_fake
+def _(A, Bt, SFA, SFB, alpha):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)

@@ -1,0 +1,189 @@
+/*
+ * gnk.h - C ABI of libgnk.so: hand-written sm_100a kernels behind the gn_kernels Python API.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA
+ * stream, allocates nothing, never throws and never exits; it returns GNK_OK (0) or a
+ * negative GNK_ERR_* code (gnk_strerror gives the text).  Outputs are caller-allocated.
+ * Kernels whose warps wait on hardware barriers bound every wait; a wait that runs out
+ * is recorded in a sticky device status word readable with gnk_device_status().
+ *
+ * "Replaces" comments name the upstream gn_kernels interface (file:line in the upstream
+ * tree) that a maintainer would rebind to the entry point.
+ *
+ * Conventions: matrices are row-major with the reduction dimension contiguous
+ * (A is [M,K], "Bt" is [N,K]; the product is A * Bt^T); ld* are row strides in ELEMENTS
+ * of the stored type (bytes for packed FP4).  stream is a cudaStream_t.
+ */
+#ifndef GNK_H_
+#define GNK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GNK_VERSION 100
+
+typedef void* gnk_stream_t; /* cudaStream_t */
+
+enum gnk_status {
+  GNK_OK = 0,
+  GNK_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, unknown enum */
+  GNK_ERR_BAD_SHAPE = -2,    /* divisibility rule of the op violated */
+  GNK_ERR_BAD_ALIGN = -3,    /* pointer or stride not aligned as the op needs */
+  GNK_ERR_ARCH = -4,         /* current device is not compute capability 10.x */
+  GNK_ERR_CUDA = -5,         /* a CUDA runtime / driver call failed (see gnk_last_cuda_error) */
+  GNK_ERR_TIMEOUT = -6,      /* a bounded device-side wait ran out (from gnk_device_status) */
+  GNK_ERR_TOO_LARGE = -7,    /* size beyond a documented maximum */
+  GNK_ERR_UNSUPPORTED = -8   /* valid request this build has no kernel for */
+};
+
+enum gnk_dtype { GNK_BF16 = 0, GNK_F16 = 1, GNK_F32 = 2 };
+enum gnk_qkind { GNK_Q_INT8 = 0, GNK_Q_E4M3 = 1, GNK_Q_E5M2 = 2, GNK_Q_E2M1 = 3 };
+enum gnk_mx_rule { GNK_MX_OCP = 0, GNK_MX_NV = 1 };
+enum gnk_out { GNK_OUT_BF16 = 0, GNK_OUT_I32 = 1 };
+
+int gnk_version(void);
+const char* gnk_strerror(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* gnk_last_cuda_error(void);
+/* Reads (and optionally clears) the sticky device status word of the current device.
+ * Synchronises the device.  *status is GNK_OK or GNK_ERR_TIMEOUT; *detail identifies the
+ * kernel role and barrier that gave up (0 if none). */
+int gnk_device_status(int* status, uint32_t* detail, int clear);
+
+/* ------------------------------------------------------------------ quantizers ---- */
+
+/* Bytes of device scratch gnk_absmax needs for n elements. */
+size_t gnk_absmax_scratch_bytes(int64_t n);
+/* out[0] = max |x[i]| as fp32.  x: contiguous n elements of `dtype`.  scratch: device
+ * memory of gnk_absmax_scratch_bytes(n) bytes, its first 4 bytes zero on entry (the
+ * kernel restores that before it ends, so one zero-initialised buffer can be reused by
+ * calls that do not overlap).
+ * Replaces: the torch reduction `x.abs().amax()` callers run before
+ * gn_kernels/quant_utils.py:162 / tests/test_quant_utils.py:10. */
+int gnk_absmax(const void* x, int dtype, int64_t n, float* out, void* scratch, gnk_stream_t stream);
+
+/* Row-wise absmax quantizer: one fp32 scale per row of `cols` contiguous elements.
+ * scale = amax/qmax (127 for INT8, 448 for E4M3); q = x / max(scale, 1e-6); INT8 rounds
+ * half-to-even and clips to [-128,127]; E4M3 clips to +-448 then rounds to nearest even.
+ * q: rows x cols bytes, contiguous.  scale: `rows` floats; when perm_h > 0 the row index
+ * r = (b*perm_l + l)*perm_h + h is stored at (b*perm_h + h)*perm_l + l instead (the
+ * [B,L,H] -> [B,H,L] transpose attention wants).  cols % 8 == 0, x 16-byte aligned rows.
+ * Replaces: benchmark_attn.py:39-51 `quantize` (+ the transpose at :77-80). */
+int gnk_quant_rowwise(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int qkind,
+                      void* q, float* scale, int64_t perm_h, int64_t perm_l, gnk_stream_t stream);
+
+/* MX quantizer: one E8M0 exponent per 32 contiguous K elements (OCP floor rule or the
+ * cuBLAS round-up rule), elements E4M3 / E5M2 (1 byte each) or E2M1 (two per byte, even
+ * element in the high nibble).  sf: [M, K/32] bytes row-major, or (sf_swizzled != 0) the
+ * 128x4-atom layout with rows padded to 128 and K/32 padded to 4 (padding written as 0).
+ * K % 32 == 0.  Replaces: gn_kernels/quant_utils.py:93-117 `quantize_mx` (+ :21-30). */
+int gnk_quant_mx(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int qkind, int rule,
+                 void* q, uint8_t* sf, int sf_swizzled, gnk_stream_t stream);
+
+/* NVFP4 quantizer: E2M1 pairs (even element in the high nibble), one E4M3 scale per 16
+ * K elements, fp32 per-tensor scale read from DEVICE memory (tensor_scale[0]).
+ *   s = e4m3(clip(amax16 / max(6*ts, 1e-12), +-448));  q = e2m1(x / max(ts*f32(s), eps))
+ * with IEEE fp32 divisions, so bytes and scales equal the torch reference bit for bit.
+ * sf layout as in gnk_quant_mx with K/16 columns.  K % 16 == 0.
+ * Replaces: gn_kernels/quant_utils.py:156-171 `quantize_nvfp4` (row-major scales) and
+ * :242-252 `quantize_nvfp4_triton` (swizzled scales). */
+int gnk_quant_nvfp4(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const float* tensor_scale,
+                    float eps, void* q, uint8_t* sf, int sf_swizzled, gnk_stream_t stream);
+
+/* Scale-factor layout conversion between row-major [M, Ks] bytes and the swizzled
+ * 128x4-atom layout [ceil128(M), ceil4(Ks)].  to_swizzled: pads with zeros.
+ * Replaces: gn_kernels/quant_utils.py:21-36 `permute_nv_sf` / `unpermute_nv_sf`. */
+int gnk_sf_swizzle(const uint8_t* src, uint8_t* dst, int64_t M, int64_t Ks, int to_swizzled, gnk_stream_t stream);
+
+/* MX / NVFP4 dequantizer to fp32 (test and debugging aid; inverse of the two above with
+ * row-major scales).  tensor_scale may be NULL (treated as 1).
+ * Replaces: gn_kernels/quant_utils.py:120-152 `dequantize_mx`. */
+int gnk_dequant_block(const void* q, const uint8_t* sf, int64_t M, int64_t K, int qkind, int block,
+                      const float* tensor_scale, float* out, gnk_stream_t stream);
+
+/* ------------------------------------------------------------------ matmuls ------- */
+
+/* C[M,N] bf16 = A[M,K] bf16 * Bt[N,K]^T, fp32 accumulate.  K % 8 == 0 (16-byte rows).
+ * Replaces: gn_kernels/cutedsl/sm100/sm100_mm_bf16.py:252-255 `mm`. */
+int gnk_mm_bf16(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc,
+                int64_t M, int64_t N, int64_t K, gnk_stream_t stream);
+
+/* INT8 x INT8 -> exact INT32 accumulate.  out_kind GNK_OUT_I32: C int32 = acc (scales and
+ * bias must be NULL).  GNK_OUT_BF16: C = bf16(f32(acc) * scale_A[m] * scale_B[n] + bias[n])
+ * evaluated in that order in fp32; any of scale_A / scale_B / bias may be NULL.
+ * K % 16 == 0.  Replaces: gn_kernels/triton_mm.py:128-171 `triton_mm` for int8 inputs. */
+int gnk_mm_i8(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc,
+              int64_t M, int64_t N, int64_t K, const float* scale_A, const float* scale_B,
+              const float* bias, int out_kind, gnk_stream_t stream);
+
+/* E4M3 x E4M3, fp32 accumulate, same row-scaled epilogue, bf16 output.  K % 16 == 0.
+ * Replaces: gn_kernels/triton_mm.py:128-171 `triton_mm` for float8_e4m3fn inputs. */
+int gnk_mm_f8(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc,
+              int64_t M, int64_t N, int64_t K, const float* scale_A, const float* scale_B,
+              const float* bias, gnk_stream_t stream);
+
+/* MXFP8: C bf16 = (A .* 2^(SFA-127)) * (Bt .* 2^(SFB-127))^T.  A, Bt E4M3; SFA, SFB E8M0
+ * in the swizzled 128x4-atom layout ([ceil128(rows), K/32] bytes).  K % 128 == 0.
+ * Replaces: gn_kernels/cutedsl/sm100/sm100_mm_mxfp8.py:380-383 `mm`. */
+int gnk_mm_mxfp8(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA,
+                 const uint8_t* SFB, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                 gnk_stream_t stream);
+
+/* NVFP4: A, Bt packed E2M1 ([rows, K/2] bytes, ld in bytes), SFA/SFB E4M3 per 16, swizzled
+ * ([ceil128(rows), K/16] bytes); alpha (host value, = tensor_scale_A * tensor_scale_B)
+ * multiplies the fp32 accumulator before the bf16 rounding.  K % 256 == 0.
+ * Replaces: gn_kernels/cutedsl/sm100/sm100_mm_nvfp4.py:383-386 `mm` (upstream has no
+ * alpha; gn_kernels/cutedsl/sm120/sm120_gated_gemm_nvfp4.py:317-319 shows where it goes). */
+int gnk_mm_nvfp4(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA,
+                 const uint8_t* SFB, float alpha, void* C, int64_t ldc, int64_t M, int64_t N,
+                 int64_t K, gnk_stream_t stream);
+
+/* FP8 with DeepSeek-style scales: SFA fp32 [M, K/128] stored M-major (element (m,kb) at
+ * SFA[kb*ld_sfa + m]), SFB fp32 [N/128, K/128] row-major (ld_sfb).  Each 128-deep partial
+ * product is scaled by SFA[m,kb]*SFB[n/128,kb] and summed in fp32; then + add[m,n] (bf16,
+ * optional) + bias[n] (bf16, optional); bf16 output.  K % 128 == 0, N % 128 == 0.
+ * Replaces: gn_kernels/cutedsl/sm120/sm120_mm_fp8_1d2d.py:307-333 `mm`. */
+int gnk_mm_f8_block128(const void* A, int64_t lda, const float* SFA, int64_t ld_sfa, const void* Bt,
+                       int64_t ldb, const float* SFB, int64_t ld_sfb, const void* bias, const void* add,
+                       int64_t ld_add, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                       gnk_stream_t stream);
+
+/* ------------------------------------------------------------------ attention ----- */
+
+/* Causal / full GQA attention forward, [B, L, H, D] layouts with D = 128 contiguous and
+ * element strides given per tensor (batch, seq, head).  qk_kind: GNK_Q_E4M3 or GNK_Q_INT8
+ * codes for Q and K with fp32 scales scale_q [B,Hq,Lq], scale_k [B,Hkv,Lk]; V and O bf16.
+ *   S = (q.k) * scale_q * scale_k * D^-1/2;  causal mask j <= i + (Lk - Lq);
+ *   O = softmax(S) V with P rounded to bf16 before P*V; rows that see no key give 0.
+ * Replaces: gn_kernels/triton_attn.py:268-325 `triton_attn` (scaled-QK path). */
+int gnk_attn_fwd(const void* q, const void* k, const void* v, void* o, const float* scale_q,
+                 const float* scale_k, int qk_kind, int64_t B, int64_t Lq, int64_t Lk, int64_t Hq,
+                 int64_t Hkv, int64_t D, const int64_t* q_strides, const int64_t* k_strides,
+                 const int64_t* v_strides, const int64_t* o_strides, int causal, gnk_stream_t stream);
+
+/* ------------------------------------------------------------------ GEMM + RS ----- */
+
+/* Number of int32 words the flags buffer of gnk_gemm_rs_bf16 must hold. */
+int64_t gnk_gemm_rs_flag_words(int64_t M, int64_t N, int world);
+
+/* K-sharded bf16 GEMM fused with a reduce-scatter along M over NVLink peer memory.
+ * x [M, K_local], w [N, K_local] (this rank's K shard).  staging[r] / flags[r]: device
+ * pointers, valid on THIS GPU, to rank r's staging buffer (world * (M/world) * N bf16) and
+ * flag words (zero before the first call; the kernel leaves them zero).  Every rank writes
+ * each finished tile into the owner's staging slot for this rank and bumps the owner's
+ * flag; the owner sums the `world` slots from its own memory in fp32 and writes
+ * output [M/world, N] bf16.  All device-side waits are bounded (GNK_ERR_TIMEOUT through
+ * gnk_device_status).  M % (128*world) == 0, N % 128 == 0, K_local % 8 == 0.
+ * Replaces: gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496 `gemm_rs`. */
+int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
+                     int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
+                     int64_t K_local, int rank, int world, uint32_t epoch, gnk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GNK_H_ */

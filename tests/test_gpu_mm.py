@@ -1,0 +1,256 @@
+"""GPU parity: tcgen05 GEMM family vs the CPU oracle, through the public Python API.
+
+INT8 results (int32 accumulators and the row-scaled bf16 epilogue) must be bit-exact.
+Floating-point kinds are bounded by max|out-ref| / max|ref| <= 1e-2 against the fp32
+dequantise-then-matmul oracle (observed errors are ~2e-3: one bf16 rounding of the output).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from gpu_util import SEED_MM, f32np, randn_bf16, rel_err, u8
+from oracle import mm as omm
+from oracle import quant as oq
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+TILES = [-1, 0, 1, 2, 3]  # automatic, 2-CTA 256x256, 128x256, 128x128, 128x64
+SHAPES = [(128, 128, 128), (256, 256, 512), (384, 512, 1024), (200, 136, 160), (1, 8, 32), (513, 264, 4096)]
+
+
+@pytest.fixture(scope="module")
+def gk():
+    import gn_kernels_b200 as g
+
+    return g
+
+
+@pytest.fixture(autouse=True)
+def _tile_reset_and_status():
+    from gn_kernels_b200 import _lib
+
+    yield
+    _lib.lib().gnk_debug_force_tile(-1)
+    _lib.raise_on_device_error()
+
+
+def force(tile):
+    from gn_kernels_b200 import _lib
+
+    assert _lib.lib().gnk_debug_force_tile(tile) == 0
+
+
+def rand_i8(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(-128, 128, shape, dtype=torch.int8, generator=g)
+
+
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_bf16(gk, tile, M, N, K):
+    K = max(K, 8) // 8 * 8
+    force(tile)
+    A = randn_bf16((M, K), 1, "cpu")
+    Bt = randn_bf16((N, K), 2, "cpu")
+    out = gk.cutedsl.sm100.sm100_mm_bf16.mm(A.cuda(), Bt.cuda().T)
+    assert rel_err(out, omm.mm_bf16(A, Bt)) <= TOL
+    out2 = gk.triton_mm(A.cuda(), Bt.cuda().T)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_int8_exact(gk, tile, M, N, K):
+    K = max(K, 16) // 16 * 16
+    force(tile)
+    A, Bt = rand_i8((M, K), 3), rand_i8((N, K), 4)
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T)
+    assert out.dtype == torch.int32
+    ref = omm.int8_mm_exact(A, Bt)
+    assert torch.equal(out.cpu(), ref)
+    g = torch.Generator().manual_seed(5)
+    sA = torch.randn(M, 1, generator=g).div(128)
+    sB = torch.randn(1, N, generator=g).div(128)
+    bias = torch.randn(N, generator=g)
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T, scale_A=sA.cuda(), scale_B=sB.cuda())
+    assert out.dtype == torch.bfloat16
+    assert torch.equal(out.cpu(), omm.mm_i8_row_scaled(A, Bt, sA, sB))
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T, bias.cuda(), scale_A=sA.cuda(), scale_B=sB.cuda())
+    assert torch.equal(out.cpu(), omm.mm_i8_row_scaled(A, Bt, sA, sB, bias))
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T, scale_B=sB.cuda())
+    assert torch.equal(out.cpu(), omm.mm_i8_row_scaled(A, Bt, None, sB))
+
+
+def test_int8_golden_and_config1(gk, golden_mm):
+    g = golden_mm
+    A, Bt = torch.from_numpy(g["i8_A"]), torch.from_numpy(g["i8_Bt"])
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T)
+    np.testing.assert_array_equal(out.cpu().numpy(), g["i8_acc"])
+    sA, sB = torch.from_numpy(g["i8_sA"]).reshape(-1, 1), torch.from_numpy(g["i8_sB"]).reshape(1, -1)
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T, scale_A=sA.cuda(), scale_B=sB.cuda())
+    torch.testing.assert_close(out.cpu(), bf16_from_bits(g["i8_scaled_ref"]), atol=4e-4, rtol=1e-2)  # upstream's own tolerance
+    # configuration 1 end to end: fp32 N(0,1) 1024^3 -> row-wise int8 -> row-scaled GEMM, all on the GPU
+    gen = torch.Generator().manual_seed(SEED_MM)
+    A32, B32 = torch.randn(1024, 1024, generator=gen), torch.randn(1024, 1024, generator=gen)
+    Aq, sA = gk.quantize_rowwise(A32.cuda(), torch.int8)
+    Bq, sB = gk.quantize_rowwise(B32.cuda(), torch.int8)
+    wAq, wsA = oq.quantize_rowwise(A32.numpy(), "int8")
+    wBq, wsB = oq.quantize_rowwise(B32.numpy(), "int8")
+    np.testing.assert_array_equal(Aq.cpu().numpy(), wAq)
+    np.testing.assert_array_equal(f32np(sB), wsB)
+    acc = gk.triton_mm(Aq, Bq.T)
+    assert torch.equal(acc.cpu(), omm.int8_mm_exact(wAq, wBq))
+    out = gk.triton_mm(Aq, Bq.T, scale_A=sA.view(-1, 1), scale_B=sB.view(1, -1))
+    assert torch.equal(out.cpu(), omm.mm_i8_row_scaled(wAq, wBq, wsA, wsB))
+
+
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_fp8_row_scaled(gk, tile, M, N, K):
+    K = max(K, 16) // 16 * 16
+    force(tile)
+    g = torch.Generator().manual_seed(6)
+    A = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    Bt = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    sA = torch.rand(M, 1, generator=g) + 0.5
+    sB = torch.rand(1, N, generator=g) + 0.5
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T)
+    assert rel_err(out, omm.mm_f8_row_scaled(u8(A), u8(Bt))) <= TOL
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T, scale_A=sA.cuda(), scale_B=sB.cuda())
+    assert rel_err(out, omm.mm_f8_row_scaled(u8(A), u8(Bt), sA, sB)) <= TOL
+
+
+def test_fp8_golden(gk, golden_mm):
+    g = golden_mm
+    A = torch.from_numpy(g["f8_A"]).view(torch.float8_e4m3fn).cuda()
+    Bt = torch.from_numpy(g["f8_Bt"]).view(torch.float8_e4m3fn).cuda()
+    out = gk.triton_mm(A, Bt.T)
+    assert rel_err(out, bf16_from_bits(g["f8_plain_ref"])) <= TOL
+    sA, sB = torch.from_numpy(g["f8_sA"]).reshape(-1, 1).cuda(), torch.from_numpy(g["f8_sB"]).reshape(1, -1).cuda()
+    out = gk.triton_mm(A, Bt.T, scale_A=sA, scale_B=sB)
+    torch.testing.assert_close(out.cpu(), bf16_from_bits(g["f8_scaled_ref"]), atol=4e-4, rtol=1e-2)
+
+
+BS_TILES = [-1, 0, 1, 2]
+BS_SHAPES = [(128, 128, 128), (256, 256, 512), (384, 512, 1024), (200, 136, 160), (16, 256, 2048), (513, 264, 4096)]
+
+
+@pytest.mark.parametrize("tile", BS_TILES)
+@pytest.mark.parametrize("M,N,K", BS_SHAPES)
+def test_mxfp8(gk, tile, M, N, K):
+    force(tile)
+    A = randn_bf16((M, K), 7)
+    Bt = randn_bf16((N, K), 8)
+    # give blocks different exponents so a misplaced scale factor cannot go unnoticed
+    A = (A.float() * torch.exp2(torch.randint(-3, 4, (M, K // 32, 1), device="cuda").float()).expand(M, K // 32, 32).reshape(M, K)).bfloat16()
+    Aq, sfa = gk.quantize_mx(A, torch.float8_e4m3fn)
+    Bq, sfb = gk.quantize_mx(Bt, torch.float8_e4m3fn)
+    out = gk.cutedsl.sm100.sm100_mm_mxfp8.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb))
+    ref = omm.mm_mxfp8(u8(Aq), u8(Bq), u8(sfa), u8(sfb))
+    assert rel_err(out, ref) <= TOL
+
+
+def test_mxfp8_golden(gk, golden_mm):
+    g = golden_mm
+    A = torch.from_numpy(g["mx_A"]).view(torch.float8_e4m3fn).cuda()
+    Bt = torch.from_numpy(g["mx_Bt"]).view(torch.float8_e4m3fn).cuda()
+    sfa = torch.from_numpy(g["mx_sfa"]).view(torch.float8_e8m0fnu).cuda()
+    sfb = torch.from_numpy(g["mx_sfb"]).view(torch.float8_e8m0fnu).cuda()
+    out = gk.cutedsl.sm100.sm100_mm_mxfp8.mm(A, Bt, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb))
+    assert rel_err(out, bf16_from_bits(g["mx_ref"])) <= TOL
+
+
+@pytest.mark.parametrize("tile", BS_TILES)
+@pytest.mark.parametrize("M,N,K", BS_SHAPES)
+def test_nvfp4(gk, tile, M, N, K):
+    K = max(K, 64) // 64 * 64
+    force(tile)
+    A = randn_bf16((M, K), 9)
+    Bt = randn_bf16((N, K), 10)
+    A = (A.float() * torch.exp2(torch.randint(-3, 4, (M, K // 16, 1), device="cuda").float()).expand(M, K // 16, 16).reshape(M, K)).bfloat16()
+    Aq, sfa, tsa = gk.quantize_nvfp4(A)
+    Bq, sfb, tsb = gk.quantize_nvfp4(Bt)
+    alpha = float(tsa) * float(tsb)
+    out = gk.cutedsl.sm100.sm100_mm_nvfp4.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb), alpha)
+    ref = omm.mm_nvfp4(u8(Aq), u8(Bq), u8(sfa), u8(sfb), np.float32(float(tsa)) * np.float32(float(tsb)))
+    assert rel_err(out, ref) <= TOL
+    # the swizzled-scale quantizer feeds the GEMM directly
+    Aq2, sfa2 = gk.quantize_nvfp4_triton(A, tsa) if K % 64 == 0 else (Aq, gk.permute_nv_sf(sfa))
+    out2 = gk.cutedsl.sm100.sm100_mm_nvfp4.mm(Aq2, Bq, sfa2, gk.permute_nv_sf(sfb), alpha)
+    assert torch.equal(out, out2)
+
+
+def _sampled_rows(M, n=64, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.sort(torch.randperm(M, generator=g)[:n]).values
+
+
+@pytest.mark.parametrize("kind", ["int8", "mxfp8", "nvfp4", "bf16"])
+def test_full_size_8192(gk, kind):
+    """Benchmark-size problems: oracle on 64 sampled rows x all columns, plus a linearity check."""
+    M = N = K = 8192
+    rows = _sampled_rows(M)
+    if kind == "int8":
+        A, Bt = rand_i8((M, K), 11), rand_i8((N, K), 12)
+        out = gk.triton_mm(A.cuda(), Bt.cuda().T)
+        assert torch.equal(out[rows.cuda()].cpu(), omm.int8_mm_exact(A[rows], Bt))
+        return
+    A = randn_bf16((M, K), SEED_MM)
+    Bt = randn_bf16((N, K), SEED_MM + 1)
+    if kind == "bf16":
+        out = gk.cutedsl.sm100.sm100_mm_bf16.mm(A, Bt.T)
+        ref = omm.mm_bf16(A[rows.cuda()].cpu(), Bt.cpu())
+    elif kind == "mxfp8":
+        Aq, sfa = gk.quantize_mx(A, torch.float8_e4m3fn)
+        Bq, sfb = gk.quantize_mx(Bt, torch.float8_e4m3fn)
+        out = gk.cutedsl.sm100.sm100_mm_mxfp8.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb))
+        r = rows.cuda()
+        ref = omm.mm_mxfp8(u8(Aq[r]), u8(Bq), u8(sfa[r]), u8(sfb))
+    else:
+        Aq, sfa, tsa = gk.quantize_nvfp4(A)
+        Bq, sfb, tsb = gk.quantize_nvfp4(Bt)
+        alpha = float(tsa) * float(tsb)
+        out = gk.cutedsl.sm100.sm100_mm_nvfp4.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb), alpha)
+        r = rows.cuda()
+        ref = omm.mm_nvfp4(u8(Aq.view(torch.uint8)[r]), u8(Bq), u8(sfa[r]), u8(sfb), np.float32(float(tsa)) * np.float32(float(tsb)))
+    assert rel_err(out[rows.cuda()], ref) <= TOL
+    # every row block was written (no tile skipped): no row of the output is all zero
+    assert bool((out.float().abs().amax(dim=1) > 0).all())
+
+
+@pytest.mark.parametrize("M", [16, 64, 128])
+def test_mxfp8_skinny_decode_shapes(gk, M):
+    N = K = 8192
+    A = randn_bf16((M, K), 31)
+    Bt = randn_bf16((N, K), 32)
+    Aq, sfa = gk.quantize_mx(A, torch.float8_e4m3fn)
+    Bq, sfb = gk.quantize_mx(Bt, torch.float8_e4m3fn)
+    out = gk.cutedsl.sm100.sm100_mm_mxfp8.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb))
+    ref = omm.mm_mxfp8(u8(Aq), u8(Bq), u8(sfa), u8(sfb))
+    assert rel_err(out, ref) <= TOL
+
+
+def test_strided_and_unaligned_operands(gk):
+    # column-major A and row-major [K,N] B are legal for triton_mm (copied into K-major form)
+    A = rand_i8((96, 80), 41).cuda()
+    B = rand_i8((80, 72), 42).cuda()  # [K, N] contiguous: NOT the fast layout
+    out = gk.triton_mm(A.T.contiguous().T, B)
+    assert torch.equal(out.cpu(), omm.int8_mm_exact(A.cpu(), B.T.contiguous().cpu()))
+    # K not a multiple of 16 bytes: padded copy
+    A = rand_i8((40, 50), 43).cuda()
+    Bt = rand_i8((24, 50), 44).cuda()
+    out = gk.triton_mm(A, Bt.T)
+    assert torch.equal(out.cpu(), omm.int8_mm_exact(A.cpu(), Bt.cpu()))
+
+
+def test_bad_arguments(gk):
+    A = torch.zeros(16, 32, dtype=torch.int8, device="cuda")
+    with pytest.raises(AssertionError):
+        gk.triton_mm(A, torch.zeros(16, 32, dtype=torch.int8, device="cuda"))
+    with pytest.raises(NotImplementedError):
+        gk.triton_mm(A.half(), A.half().T)
+    with pytest.raises(RuntimeError):
+        gk.triton_mm(A.cpu(), A.cpu().T)
