@@ -29,7 +29,7 @@ _SIGNATURES = {
     "gnk_last_cuda_error": (c_char_p, []),
     "gnk_device_status": (c_int, [POINTER(c_int), POINTER(c_uint32), c_int]),
     "gnk_absmax_scratch_bytes": (c_size_t, [c_int64]),
-    "gnk_absmax": (c_int, [_P, c_int, c_int64, _P, _P, _P]),
+    "gnk_absmax": (c_int, [_P, c_int, c_int64, c_float, _P, _P, _P]),
     "gnk_quant_rowwise": (c_int, [_P, c_int, c_int64, c_int64, c_int64, c_int, _P, _P, c_int64, c_int64, _P]),
     "gnk_quant_mx": (c_int, [_P, c_int, c_int64, c_int64, c_int64, c_int, c_int, _P, _P, c_int, _P]),
     "gnk_quant_nvfp4": (c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_float, _P, _P, c_int, _P]),
@@ -41,6 +41,8 @@ _SIGNATURES = {
     "gnk_mm_mxfp8": (c_int, [_P, c_int64, _P, c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_mm_nvfp4": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_float, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_debug_force_tile": (c_int, [c_int]),
+    "gnk_debug_max_clusters": (c_int, [c_int]),
+    "gnk_debug_trace": (c_int, [_P]),
 }
 
 

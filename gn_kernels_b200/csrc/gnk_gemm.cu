@@ -23,6 +23,7 @@ namespace gnk {
 namespace {
 
 enum Epi { EPI_BF16 = 0, EPI_ROWSCALED = 1, EPI_I32 = 2 };
+constexpr int kTraceEvents = 256;  // stages recorded per (CTA, role) when tracing
 
 template <MmaKind K> struct KindInfo;
 template <> struct KindInfo<MmaKind::F16> { static constexpr bool kBlockScaled = false; static constexpr int kSfPerStage = 0; };
@@ -43,6 +44,7 @@ struct GemmArgs {
   const float* bias;
   float alpha;
   int vec_ok;  // C rows 16-byte aligned: vector stores allowed
+  long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
 };
 
 template <MmaKind KIND, int BN, int CG>
@@ -169,6 +171,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(192, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  int trace_it = 0;
   const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
@@ -204,46 +207,69 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(192, 1)
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
+  // Producer and MMA warps run their loops warp-uniformly (all 32 lanes wait on the barriers and
+  // compute addresses and descriptors, which keeps those values in uniform registers); one
+  // elected lane executes the TMA / tcgen05 issue instructions.
   if (warp == 4) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      uint32_t stage = 0, parity = 1;
-      bool ok = true;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        int tm, tn;
-        tile_coords(t, g.tiles_m, g.tiles_n, tm, tn);
-        const int a_row = (tm * CG + cta_rank) * 128;
-        const int b_row = tn * BN + cta_rank * (BN / CG);
-        for (int k = 0; k < g.k_iters; ++k) {
-          if (!mbar_wait(bar_empty(stage), parity, (1u << 24) | (1u << 16) | stage)) { ok = false; break; }
-          // both CTAs of a pair count their bytes on CTA 0's barrier
-          const uint32_t full = CG == 2 ? map_to_cta(bar_full(stage), 0) : bar_full(stage);
+    const bool leader = elect_one();
+    uint32_t stage = 0, parity = 1;
+    bool ok = true;
+    // both CTAs of a pair count their bytes on CTA 0's barrier
+    const uint32_t full0 = CG == 2 ? map_to_cta(bar_full(0), 0) : bar_full(0);
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int tm, tn;
+      tile_coords(t, g.tiles_m, g.tiles_n, tm, tn);
+      const int a_row = (tm * CG + cta_rank) * 128;
+      const int b_row = tn * BN + cta_rank * (BN / CG);
+      const int sfa_row = tm * CG + cta_rank;
+      const int sfb_row = (tn * BN) / 128;
+      for (int k = 0; k < g.k_iters; ++k) {
+        const long long tr0 = g.trace ? clock64() : 0;
+        if (!mbar_wait(bar_empty(stage), parity, (1u << 24) | (1u << 16) | stage)) { ok = false; break; }
+        const long long tr1 = g.trace ? clock64() : 0;
+        const uint32_t full = full0 + 8 * stage;
+        const uint32_t sa = stage_a(stage), sb = stage_b(stage);
+        if (leader) {
           if constexpr (CG == 2) {
             mbar_expect_tx_cluster(full, C::kStageBytes);
-            tma_load_2d_pair(stage_a(stage), &tm_a, full, k * kInner, a_row);
-            tma_load_2d_pair(stage_b(stage), &tm_b, full, k * kInner, b_row);
+            tma_load_2d_pair(sa, &tm_a, full, k * kInner, a_row);
+            tma_load_2d_pair(sb, &tm_b, full, k * kInner, b_row);
             if constexpr (kBS) {
-              tma_load_2d_pair(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), tm * CG + cta_rank);
-              tma_load_2d_pair(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), tn * C::kSfbGroups);
+              tma_load_2d_pair(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
+              tma_load_2d_pair(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), sfb_row);
             }
           } else {
             mbar_expect_tx(full, C::kStageBytes);
-            tma_load_2d(stage_a(stage), &tm_a, full, k * kInner, a_row);
-            tma_load_2d(stage_b(stage), &tm_b, full, k * kInner, b_row);
+            tma_load_2d(sa, &tm_a, full, k * kInner, a_row);
+            tma_load_2d(sb, &tm_b, full, k * kInner, b_row);
             if constexpr (kBS) {
-              tma_load_2d(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), tm);
-              tma_load_2d(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), (tn * BN) / 128);
+              tma_load_2d(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
+              tma_load_2d(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), sfb_row);
             }
           }
-          if (++stage == S) { stage = 0; parity ^= 1; }
+          if (g.trace && blockIdx.x < 2 && trace_it < kTraceEvents) {
+            long long* tp = g.trace + ((blockIdx.x * 2 + 0) * kTraceEvents + trace_it) * 3;
+            tp[0] = tr0; tp[1] = tr1; tp[2] = clock64();
+          }
         }
+        ++trace_it;
+        __syncwarp();
+        if (++stage == S) { stage = 0; parity ^= 1; }
       }
     }
   } else if (warp == 5) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0 && cta_rank == 0) {
+    if (cta_rank == 0) {
+      const bool leader = elect_one();
       uint32_t stage = 0, parity = 0, acc = 0, acc_parity = 1, iter = 0;
       bool ok = true;
+      constexpr uint32_t kIdesc = KIND == MmaKind::F16      ? idesc_dense(1, 1, 1, 128 * CG, BN)
+                                  : KIND == MmaKind::I8     ? idesc_dense(2, 1, 1, 128 * CG, BN)
+                                  : KIND == MmaKind::F8F6F4 ? idesc_dense(1, 0, 0, 128 * CG, BN)
+                                  : KIND == MmaKind::MXF8F6F4 ? idesc_block_scaled(0, 1, 128 * CG, BN)
+                                                              : idesc_block_scaled(1, 0, 128 * CG, BN);
+      const uint32_t sf_tmem = tmem_base + C::kSfBase;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
         if (!mbar_wait(bar_tempty(acc), acc_parity, (2u << 24) | (2u << 16) | acc)) { ok = false; break; }
         if constexpr (C::kOverlap) {
@@ -252,47 +278,57 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(192, 1)
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
         for (int k = 0; k < g.k_iters; ++k) {
+          const long long tr0 = g.trace ? clock64() : 0;
           if (!mbar_wait(bar_full(stage), parity, (2u << 24) | (4u << 16) | stage)) { ok = false; break; }
+          const long long tr1 = g.trace ? clock64() : 0;
           tc_fence_after();
           const uint64_t a_desc = sdesc_k128(stage_a(stage));
           const uint64_t b_desc = sdesc_k128(stage_b(stage));
-          if constexpr (kBS) {
-            constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per stage: 1 (mxfp8) or 4 (nvfp4)
+          const uint64_t sfa_desc = sdesc_sf(stage_sfa(stage));
+          const uint64_t sfb_desc = sdesc_sf(stage_sfb(stage));
+          const uint32_t empty = bar_empty(stage);
+          if (leader) {
+            if constexpr (kBS) {
+              constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per stage: 1 (mxfp8) or 4 (nvfp4)
 #pragma unroll
-            for (int a = 0; a < kAtoms; ++a) {
-              tc_cp_sf<CG>(tmem_base + C::kSfBase + 4 * a, sdesc_sf(stage_sfa(stage) + 512 * a));
+              for (int a = 0; a < kAtoms; ++a) {
+                tc_cp_sf<CG>(sf_tmem + 4 * a, sfa_desc + (512 >> 4) * a);
 #pragma unroll
-              for (int j = 0; j < C::kSfbGroups; ++j)
-                tc_cp_sf<CG>(tmem_base + C::kSfBase + C::kSfaCols + (a * C::kSfbGroups + j) * 4,
-                             sdesc_sf(stage_sfb(stage) + j * C::kSfAtomBytes + 512 * a));
+                for (int j = 0; j < C::kSfbGroups; ++j)
+                  tc_cp_sf<CG>(sf_tmem + C::kSfaCols + (a * C::kSfbGroups + j) * 4,
+                               sfb_desc + ((j * C::kSfAtomBytes + 512 * a) >> 4));
+              }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint32_t accum = (k | kk) != 0;
+              if constexpr (!kBS) {
+                tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, accum);
+              } else if constexpr (KIND == MmaKind::MXF8F6F4) {
+                // the four K steps of a stage read bytes 0..3 of the same scale columns (scale ids in the descriptor)
+                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc | (kk << 4) | (kk << 29), sf_tmem,
+                                    sf_tmem + C::kSfaCols, accum);
+              } else {
+                // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
+                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, sf_tmem + 4 * kk,
+                                    sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4, accum);
+              }
+            }
+            if constexpr (CG == 2) tc_commit_pair(empty, 3); else tc_commit<1>(empty);
+            if (g.trace && blockIdx.x < 2 && trace_it < kTraceEvents) {
+              long long* tp = g.trace + ((blockIdx.x * 2 + 1) * kTraceEvents + trace_it) * 3;
+              tp[0] = tr0; tp[1] = tr1; tp[2] = clock64();
             }
           }
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t accum = (k | kk) != 0;
-            if constexpr (KIND == MmaKind::F16) {
-              tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc_dense(1, 1, 1, 128 * CG, BN), accum);
-            } else if constexpr (KIND == MmaKind::I8) {
-              tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc_dense(2, 1, 1, 128 * CG, BN), accum);
-            } else if constexpr (KIND == MmaKind::F8F6F4) {
-              tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc_dense(1, 0, 0, 128 * CG, BN), accum);
-            } else if constexpr (KIND == MmaKind::MXF8F6F4) {
-              // the four K steps of a stage read bytes 0..3 of the same scale columns
-              tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk,
-                                  idesc_block_scaled(0, 1, 128 * CG, BN, kk, kk), tmem_base + C::kSfBase,
-                                  tmem_base + C::kSfBase + C::kSfaCols, accum);
-            } else {
-              // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
-              tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc_block_scaled(1, 0, 128 * CG, BN),
-                                  tmem_base + C::kSfBase + 4 * kk,
-                                  tmem_base + C::kSfBase + C::kSfaCols + kk * C::kSfbGroups * 4, accum);
-            }
-          }
-          if constexpr (CG == 2) tc_commit_pair(bar_empty(stage), 3); else tc_commit<1>(bar_empty(stage));
+          ++trace_it;
+          __syncwarp();
           if (++stage == S) { stage = 0; parity ^= 1; }
         }
         if (!ok) break;
-        if constexpr (CG == 2) tc_commit_pair(bar_tfull(acc), 3); else tc_commit<1>(bar_tfull(acc));
+        if (leader) {
+          if constexpr (CG == 2) tc_commit_pair(bar_tfull(acc), 3); else tc_commit<1>(bar_tfull(acc));
+        }
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_parity ^= 1;
       }
@@ -342,6 +378,9 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(192, 1)
   }
 }
 
+long long* g_trace = nullptr;  // test hook (gnk_debug_trace): device buffer of 2*2*256*3 int64
+int g_max_clusters = 0;  // test hook (gnk_debug_max_clusters): cap on the persistent grid, 0 = none
+
 template <MmaKind KIND>
 struct ElemInfo {
   // bytes per K element as a rational: bf16 2/1, 8-bit 1/1, fp4 1/2
@@ -384,16 +423,38 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   g.tiles_m = static_cast<int>((M + 128 * CG - 1) / (128 * CG));
   g.tiles_n = static_cast<int>((N + BN - 1) / BN);
   const int tiles = g.tiles_m * g.tiles_n;
-  int clusters = num_sms() / CG;
-  if (clusters > tiles) clusters = tiles;
   auto kern = gemm_kernel<KIND, BN, CG, EPI>;
-  static bool attr_set[64];  // per instantiation, per device
+  // Persistent grid = the number of clusters that can be resident at once.  For 2-CTA
+  // clusters this can be below SMs / 2 (both CTAs must land on one SM pair), and a cluster
+  // that does not fit the first wave would run its whole share of tiles after everyone else.
+  static int resident[64];  // per instantiation, per device; 0 = not yet queried
   int dev = 0;
   GNK_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+  if (dev < 0 || dev >= 64) return GNK_ERR_UNSUPPORTED;
+  if (resident[dev] == 0) {
     GNK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    int n = num_sms() / CG;
+    if (CG > 1) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(num_sms() / CG * CG));
+      cfg.blockDim = dim3(192);
+      cfg.dynamicSmemBytes = C::kSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = CG;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int q = 0;
+      GNK_CUDA_OK(cudaOccupancyMaxActiveClusters(&q, kern, &cfg));
+      if (q > 0 && q < n) n = q;
+    }
+    resident[dev] = n;
   }
+  int clusters = resident[dev];
+  if (g_max_clusters > 0 && clusters > g_max_clusters) clusters = g_max_clusters;
+  if (clusters > tiles) clusters = tiles;
   kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, g);
   GNK_LAUNCH_OK();
   return GNK_OK;
@@ -445,6 +506,7 @@ GemmArgs base_args(void* C, int64_t ldc, int64_t M, int64_t N, int out_elem_byte
   g.ldc = ldc;
   g.alpha = 1.f;
   g.vec_ok = aligned16(C) && ((ldc * out_elem_bytes) % 16 == 0);
+  g.trace = g_trace;
   return g;
 }
 
@@ -459,6 +521,17 @@ using namespace gnk;
 extern "C" int gnk_debug_force_tile(int sel) {
   if (sel < -1 || sel > 3) return GNK_ERR_BAD_ARG;
   g_force_tile = sel;
+  return GNK_OK;
+}
+
+// Debug: device buffer (2 CTAs x 2 roles x 256 stages x 3 int64 clock stamps) or NULL to stop tracing.
+extern "C" int gnk_debug_trace(void* device_buffer) {
+  g_trace = static_cast<long long*>(device_buffer);
+  return GNK_OK;
+}
+
+extern "C" int gnk_debug_max_clusters(int n) {
+  g_max_clusters = n < 0 ? 0 : n;
   return GNK_OK;
 }
 

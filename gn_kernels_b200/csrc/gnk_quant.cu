@@ -93,7 +93,16 @@ template <typename T>
 __device__ __forceinline__ float absmax_partial(const T* __restrict__ x, int64_t n) {
   float m = 0.f;
   const int64_t nvec = n >> 3;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {  // four independent 16-byte loads in flight
+    float v[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) load8<T>(x + (i + j * stride) * 8, v[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m = fmaxf(m, amax8(v[j]));
+  }
+  for (; i < nvec; i += stride) {
     float v[8];
     load8<T>(x + i * 8, v);
     m = fmaxf(m, amax8(v));
@@ -107,7 +116,7 @@ __device__ __forceinline__ float absmax_partial(const T* __restrict__ x, int64_t
 // scratch[0] = ticket (zero on entry, zero again on exit), scratch[1 + cta] = partial maxima
 template <typename T>
 __global__ void __launch_bounds__(kAbsmaxThreads) absmax_kernel(const T* __restrict__ x, int64_t n,
-                                                                float* __restrict__ out,
+                                                                float* __restrict__ out, float divisor,
                                                                 unsigned int* __restrict__ scratch) {
   __shared__ float warp_max[kAbsmaxThreads / 32];
   __shared__ bool is_last;
@@ -134,7 +143,7 @@ __global__ void __launch_bounds__(kAbsmaxThreads) absmax_kernel(const T* __restr
   if (threadIdx.x == 0) {
     float b = warp_max[0];
     for (int i = 1; i < kAbsmaxThreads / 32; ++i) b = fmaxf(b, warp_max[i]);
-    out[0] = b;
+    out[0] = __fdiv_rn(b, divisor);
     scratch[0] = 0u;
   }
 }
@@ -363,8 +372,9 @@ using namespace gnk;
 
 extern "C" size_t gnk_absmax_scratch_bytes(int64_t) { return sizeof(unsigned int) * (1 + kAbsmaxMaxCtas); }
 
-extern "C" int gnk_absmax(const void* x, int dtype, int64_t n, float* out, void* scratch, gnk_stream_t stream) {
-  if (!x || !out || !scratch || n <= 0) return GNK_ERR_BAD_ARG;
+extern "C" int gnk_absmax(const void* x, int dtype, int64_t n, float divisor, float* out, void* scratch,
+                          gnk_stream_t stream) {
+  if (!x || !out || !scratch || n <= 0 || !(divisor > 0.f)) return GNK_ERR_BAD_ARG;
   if (!aligned16(x)) return GNK_ERR_BAD_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int64_t want = (n / 8 + kAbsmaxThreads - 1) / kAbsmaxThreads;
@@ -374,7 +384,7 @@ extern "C" int gnk_absmax(const void* x, int dtype, int64_t n, float* out, void*
   if (grid > kAbsmaxMaxCtas) grid = kAbsmaxMaxCtas;
   return dispatch_dtype(dtype, [&](auto* tag) -> int {
     using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
-    absmax_kernel<T><<<grid, kAbsmaxThreads, 0, st>>>(static_cast<const T*>(x), n, out,
+    absmax_kernel<T><<<grid, kAbsmaxThreads, 0, st>>>(static_cast<const T*>(x), n, out, divisor,
                                                        static_cast<unsigned int*>(scratch));
     GNK_LAUNCH_OK();
     return (int)GNK_OK;

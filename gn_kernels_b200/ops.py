@@ -46,18 +46,19 @@ def _ceil(a: int, b: int) -> int:
 
 # ------------------------------------------------------------------ quantizers
 @torch.library.custom_op("gnk::absmax", mutates_args=())
-def absmax(x: Tensor) -> Tensor:
+def absmax(x: Tensor, divisor: float = 1.0) -> Tensor:
+    """max |x| / divisor (correctly rounded fp32 division) as a 0-dim tensor."""
     _need_cuda(x)
     x = x.contiguous()
     out = torch.empty((), dtype=torch.float32, device=x.device)
     scratch = torch.zeros(lib().gnk_absmax_scratch_bytes(x.numel()) // 4, dtype=torch.int32, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib().gnk_absmax(_p(x), _DT[x.dtype], x.numel(), _p(out), _p(scratch), _stream(x)), "gnk_absmax")
+        check(lib().gnk_absmax(_p(x), _DT[x.dtype], x.numel(), divisor, _p(out), _p(scratch), _stream(x)), "gnk_absmax")
     return out
 
 
 @absmax.register_fake
-def _(x):
+def _(x, divisor=1.0):
     return x.new_empty((), dtype=torch.float32)
 
 
@@ -181,19 +182,27 @@ def _(q, sf, block, tensor_scale):
 
 
 # ------------------------------------------------------------------ matmuls
-def _k_major(t: Tensor, align_bytes: int = 16) -> Tensor:
-    """Returns t ([rows, K]) with K contiguous and a 16-byte aligned row pitch, copying if needed."""
-    if t.stride(-1) == 1 and (t.stride(0) * t.element_size()) % align_bytes == 0 and t.data_ptr() % 16 == 0:
+def _k_major(t: Tensor, k_pad: int = 0) -> Tensor:
+    """Returns t ([rows, K]) with K contiguous, a 16-byte aligned base and row pitch, and
+    `k_pad` extra zero columns (a device copy is made only when one of these does not hold)."""
+    ok = t.stride(-1) == 1 and (t.stride(0) * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
+    if ok and k_pad == 0:
         return t
-    K = t.shape[1]
-    per = align_bytes // t.element_size()
-    Kp = _ceil(K, per)
-    if Kp == K:
+    if k_pad == 0:
         return t.contiguous()
-    buf = torch.zeros((t.shape[0], Kp), dtype=torch.uint8 if t.element_size() == 1 else t.dtype, device=t.device)
-    buf = buf.view(t.dtype) if t.element_size() == 1 else buf
-    buf[:, :K] = t
-    return buf[:, :K]
+    rows, K = t.shape
+    buf = torch.zeros((rows, K + k_pad), dtype=torch.uint8, device=t.device).view(t.dtype) if t.element_size() == 1 else torch.zeros(
+        (rows, K + k_pad), dtype=t.dtype, device=t.device
+    )
+    buf[:, :K].copy_(t)
+    return buf
+
+
+def _prep_ab(A: Tensor, Bt: Tensor, k_multiple: int) -> tuple[Tensor, Tensor, int]:
+    """K-major operands whose K is a multiple of `k_multiple` elements (zero padding adds nothing to the product)."""
+    K = A.shape[1]
+    pad = (-K) % k_multiple
+    return _k_major(A, pad), _k_major(Bt, pad), K + pad
 
 
 @torch.library.custom_op("gnk::mm_bf16", mutates_args=())
@@ -201,7 +210,7 @@ def mm_bf16(A: Tensor, Bt: Tensor) -> Tensor:
     _need_cuda(A, Bt)
     M, K = A.shape
     N = Bt.shape[0]
-    A, Bt = _k_major(A), _k_major(Bt)
+    A, Bt, K = _prep_ab(A, Bt, 8)
     C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
     with torch.cuda.device(A.device):
         check(lib().gnk_mm_bf16(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(C), N, M, N, K, _stream(A)), "gnk_mm_bf16")
@@ -218,7 +227,7 @@ def mm_i8(A: Tensor, Bt: Tensor, scale_A: Tensor | None, scale_B: Tensor | None,
     _need_cuda(A, Bt)
     M, K = A.shape
     N = Bt.shape[0]
-    A, Bt = _k_major(A), _k_major(Bt)
+    A, Bt, K = _prep_ab(A, Bt, 16)
     C = torch.empty((M, N), dtype=torch.int32 if out_i32 else torch.bfloat16, device=A.device)
     f = lambda t: t.to(torch.float32).contiguous() if t is not None else None  # noqa: E731
     sa, sb, bi = f(scale_A), f(scale_B), f(bias)
@@ -241,7 +250,7 @@ def mm_f8(A: Tensor, Bt: Tensor, scale_A: Tensor | None, scale_B: Tensor | None,
     _need_cuda(A, Bt)
     M, K = A.shape
     N = Bt.shape[0]
-    A, Bt = _k_major(A), _k_major(Bt)
+    A, Bt, K = _prep_ab(A, Bt, 16)
     C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
     f = lambda t: t.to(torch.float32).contiguous() if t is not None else None  # noqa: E731
     sa, sb, bi = f(scale_A), f(scale_B), f(bias)

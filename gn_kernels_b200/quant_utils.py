@@ -59,7 +59,7 @@ def quantize_nvfp4(x: Tensor, tensor_scale: Tensor | None = None, eps: float = 1
     Upstream gn_kernels/quant_utils.py:156-171.  Returns (xq fp4x2 [M, K/2], scales, tensor_scale)."""
     assert x.ndim == 2 and x.shape[1] % 16 == 0
     if tensor_scale is None:
-        tensor_scale = ops.absmax(x) / (448.0 * 6.0)
+        tensor_scale = ops.absmax(x, 448.0 * 6.0)  # one kernel; torch's scalar division on CUDA is not IEEE
     elif not isinstance(tensor_scale, Tensor):
         tensor_scale = torch.tensor(float(tensor_scale), dtype=torch.float32, device=x.device)
     xq, sf = ops.quant_nvfp4(x, tensor_scale, eps, False)

@@ -58,13 +58,15 @@ int gnk_device_status(int* status, uint32_t* detail, int clear);
 
 /* Bytes of device scratch gnk_absmax needs for n elements. */
 size_t gnk_absmax_scratch_bytes(int64_t n);
-/* out[0] = max |x[i]| as fp32.  x: contiguous n elements of `dtype`.  scratch: device
+/* out[0] = max |x[i]| / divisor as fp32 (IEEE division; divisor 1 gives the plain maximum,
+ * 2688 = 448*6 gives the NVFP4 tensor scale).  x: contiguous n elements of `dtype`.  scratch: device
  * memory of gnk_absmax_scratch_bytes(n) bytes, its first 4 bytes zero on entry (the
  * kernel restores that before it ends, so one zero-initialised buffer can be reused by
  * calls that do not overlap).
  * Replaces: the torch reduction `x.abs().amax()` callers run before
  * gn_kernels/quant_utils.py:162 / tests/test_quant_utils.py:10. */
-int gnk_absmax(const void* x, int dtype, int64_t n, float* out, void* scratch, gnk_stream_t stream);
+int gnk_absmax(const void* x, int dtype, int64_t n, float divisor, float* out, void* scratch,
+               gnk_stream_t stream);
 
 /* Row-wise absmax quantizer: one fp32 scale per row of `cols` contiguous elements.
  * scale = amax/qmax (127 for INT8, 448 for E4M3); q = x / max(scale, 1e-6); INT8 rounds

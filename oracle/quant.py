@@ -61,14 +61,22 @@ def f32_to_e4m3(x: np.ndarray) -> np.ndarray:
     return out.astype(np.uint8)
 
 
-def e4m3_to_f32(b: np.ndarray) -> np.ndarray:
-    b = np.asarray(b, dtype=np.uint8).astype(np.int32)
+def _e4m3_table() -> np.ndarray:
+    b = np.arange(256, dtype=np.int32)
     sign = np.where(b & 0x80, -1.0, 1.0)
     e = (b >> 3) & 0xF
     m = b & 0x7
     val = np.where(e == 0, m * 2.0**-9, (1.0 + m / 8.0) * np.exp2(e.astype(np.float64) - 7))
     val = np.where((b & 0x7F) == 0x7F, np.nan, val)
     return (sign * val).astype(F32)
+
+
+_E4M3_LUT = _e4m3_table()
+
+
+def e4m3_to_f32(b: np.ndarray) -> np.ndarray:
+    """E4M3 encodings -> float32 (sign, 4-bit exponent biased by 7, 3-bit mantissa; 0x7F/0xFF are NaN)."""
+    return _E4M3_LUT[np.asarray(b, dtype=np.uint8)]
 
 
 def f32_to_e5m2(x: np.ndarray) -> np.ndarray:
