@@ -81,6 +81,29 @@ int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uin
   return GNK_OK;
 }
 
+int make_tmap_4d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, const uint64_t dims[4],
+                 const uint64_t strides_bytes[3], const uint32_t box[4], CUtensorMapSwizzle swz) {
+  auto fn = encode_fn();
+  if (!fn) {
+    snprintf(tl_cuda_error, sizeof(tl_cuda_error), "cuTensorMapEncodeTiled entry point not found");
+    return GNK_ERR_CUDA;
+  }
+  if (!aligned16(base)) return GNK_ERR_BAD_ALIGN;
+  for (int i = 0; i < 3; ++i)
+    if (strides_bytes[i] & 15) return GNK_ERR_BAD_ALIGN;
+  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstride[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estride[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dt, 4, const_cast<void*>(base), gdim, gstride, bx, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(tl_cuda_error, sizeof(tl_cuda_error), "cuTensorMapEncodeTiled (rank 4) failed (%d)", (int)r);
+    return GNK_ERR_CUDA;
+  }
+  return GNK_OK;
+}
+
 static std::vector<status_reader_t>& readers() {
   static std::vector<status_reader_t> v;
   return v;

@@ -45,6 +45,10 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t cols,
                  uint64_t ld_bytes, uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz);
 
+// Rank-4 tiled descriptor: dims / box innermost first, strides_bytes for dims 1..3.
+int make_tmap_4d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, const uint64_t dims[4],
+                 const uint64_t strides_bytes[3], const uint32_t box[4], CUtensorMapSwizzle swz);
+
 // Each translation unit with bounded waits owns a sticky device status word (first failure
 // wins; detail = (role << 24) | (barrier << 16) | extra) and registers a reader for it.
 typedef int (*status_reader_t)(unsigned int* words, int clear);

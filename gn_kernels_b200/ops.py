@@ -316,3 +316,42 @@ def mm_nvfp4(A: Tensor, Bt: Tensor, SFA: Tensor, SFB: Tensor, alpha: float) -> T
 @mm_nvfp4.register_fake
 def _(A, Bt, SFA, SFB, alpha):
     return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)
+
+
+# ------------------------------------------------------------------ attention
+def _blhd_ok(t: Tensor) -> bool:
+    es = t.element_size()
+    return t.stride(-1) == 1 and all((t.stride(i) * es) % 16 == 0 for i in range(3)) and t.data_ptr() % 16 == 0
+
+
+@torch.library.custom_op("gnk::attn_fwd", mutates_args=())
+def attn_fwd(q: Tensor, k: Tensor, v: Tensor, scale_q: Tensor | None, scale_k: Tensor | None, causal: bool) -> Tensor:
+    """q [B,Lq,Hq,D], k [B,Lk,Hkv,D] int8 or float8_e4m3fn; v [B,Lk,Hkv,D] bf16; scales fp32 [B,H,L]."""
+    _need_cuda(q, k, v)
+    B, Lq, Hq, D = q.shape
+    _, Lk, Hkv, _ = k.shape
+    if q.dtype not in (torch.int8, torch.float8_e4m3fn) or k.dtype != q.dtype:
+        raise NotImplementedError(f"attention needs int8 or float8_e4m3fn Q and K (got {q.dtype}, {k.dtype})")
+    if v.dtype != torch.bfloat16:
+        raise NotImplementedError("attention needs bf16 V")
+    q = q if _blhd_ok(q) else q.contiguous()
+    k = k if _blhd_ok(k) else k.contiguous()
+    v = v if _blhd_ok(v) else v.contiguous()
+    sq = scale_q.to(torch.float32).contiguous() if scale_q is not None else None
+    sk = scale_k.to(torch.float32).contiguous() if scale_k is not None else None
+    o = torch.empty((B, Lq, Hq, D), dtype=torch.bfloat16, device=q.device)
+    I3 = ctypes.c_int64 * 3
+    strides = [I3(*t.stride()[:3]) for t in (q, k, v, o)]
+    with torch.cuda.device(q.device):
+        check(
+            lib().gnk_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(sq), _p(sk), _QK[q.dtype], B, Lq, Lk, Hq, Hkv, D,
+                               strides[0], strides[1], strides[2], strides[3], int(causal), _stream(q)),
+            "gnk_attn_fwd",
+        )
+    return o
+
+
+@attn_fwd.register_fake
+def _(q, k, v, scale_q, scale_k, causal):
+    B, Lq, Hq, D = q.shape
+    return q.new_empty((B, Lq, Hq, D), dtype=torch.bfloat16)

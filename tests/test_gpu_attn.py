@@ -1,0 +1,124 @@
+"""GPU parity: tcgen05 attention forward (8-bit QK + scales, bf16 V) vs the CPU oracle.
+
+Bound: max|out-ref| / max|ref| <= 1e-2 against the fp32 dequantise-then-softmax oracle, plus
+the upstream test's own elementwise tolerance (rtol 1.6e-2, atol 1e-3,
+tests/test_triton_attn.py:41) loosened only by the bf16 rounding of P that upstream's kernel
+also performs."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from gpu_util import SEED_ATTN, rel_err, u8
+from oracle import attn as oattn
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def gk():
+    import gn_kernels_b200 as g
+
+    return g
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from gn_kernels_b200 import _lib
+
+    yield
+    _lib.raise_on_device_error()
+
+
+def run_case(gk, q, k, v, dt, causal):
+    kind = "int8" if dt == torch.int8 else "e4m3"
+    qq, sq = gk.quantize_rowwise(q, dt, transpose_scales=True)
+    kq, sk = gk.quantize_rowwise(k, dt, transpose_scales=True)
+    out = gk.triton_attn(qq, kq, v, sq, sk, causal=causal)
+    codes = (lambda t: t.cpu().numpy()) if dt == torch.int8 else u8
+    ref = oattn.attention_qk_quantized(codes(qq), codes(kq), v, sq, sk, kind=kind, causal=causal)
+    return out, ref
+
+
+@pytest.mark.parametrize("dt", [torch.float8_e4m3fn, torch.int8])
+@pytest.mark.parametrize("shape", ["64x256", "128x32", "33x123", "257x39"])  # upstream tests/test_triton_attn.py:25
+@pytest.mark.parametrize("causal", [False, True])
+def test_upstream_shapes_golden_inputs(gk, golden_attn, dt, shape, causal):
+    g = golden_attn
+    q, k, v = (bf16_from_bits(g[f"{shape}_{n}"]).cuda() for n in "qkv")
+    out, ref = run_case(gk, q, k, v, dt, causal)
+    assert out.shape == ref.shape and out.dtype == torch.bfloat16
+    assert rel_err(out, ref) <= TOL
+    torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=1.6e-2, atol=4e-3)
+    # against the upstream test oracle on the UNquantised inputs: quantisation noise only
+    sdpa = bf16_from_bits(g[f"{shape}_o_{int(causal)}"])
+    assert rel_err(out, sdpa) <= 5e-2
+
+
+@pytest.mark.parametrize("dt", [torch.float8_e4m3fn, torch.int8])
+@pytest.mark.parametrize("B,Lq,Lk,Hq,Hkv", [(2, 256, 256, 8, 4), (1, 384, 1000, 4, 1), (2, 1, 130, 2, 2), (1, 129, 129, 6, 3), (1, 512, 128, 4, 4)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_shapes(gk, dt, B, Lq, Lk, Hq, Hkv, causal):
+    g = torch.Generator().manual_seed(Lq * 7 + Lk)
+    q = torch.randn(B, Lq, Hq, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Lk, Hkv, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(B, Lk, Hkv, 128, generator=g).bfloat16().cuda()
+    out, ref = run_case(gk, q, k, v, dt, causal)
+    assert rel_err(out, ref) <= TOL
+    if causal and Lq > Lk:  # rows that see no key are zero (upstream triton_attn.py:236-237)
+        assert not out[:, : Lq - Lk].float().abs().any()
+
+
+def test_peaked_scores_exercise_rescale(gk):
+    # large logits: row maxima jump by far more than the lazy-rescale threshold between tiles
+    g = torch.Generator().manual_seed(5)
+    q = (torch.randn(1, 256, 2, 128, generator=g) * 4).bfloat16().cuda()
+    k = (torch.randn(1, 1024, 2, 128, generator=g) * 4).bfloat16().cuda()
+    k[:, 900:] *= 3
+    v = torch.randn(1, 1024, 2, 128, generator=g).bfloat16().cuda()
+    for causal in (False, True):
+        out, ref = run_case(gk, q, k, v, torch.float8_e4m3fn, causal)
+        assert rel_err(out, ref) <= TOL
+
+
+def test_unscaled_and_strided(gk):
+    g = torch.Generator().manual_seed(9)
+    q = (torch.randn(1, 200, 4, 128, generator=g) * 0.5).cuda().to(torch.float8_e4m3fn)
+    k = (torch.randn(1, 300, 2, 128, generator=g) * 0.5).cuda().to(torch.float8_e4m3fn)
+    vbig = torch.randn(1, 300, 2, 256, generator=g).bfloat16().cuda()
+    v = vbig[..., :128]  # strided view: last dim contiguous, other strides arbitrary (upstream :281-286)
+    out = gk.triton_attn(q, k, v, causal=True)
+    ref = oattn.attention_f32(q.float().cpu(), k.float().cpu(), v.cpu(), causal=True).bfloat16()
+    assert rel_err(out, ref) <= TOL
+
+
+def test_benchmark_configuration_subset(gk):
+    """Configuration 4 (B=4, Hq=32, Hkv=8, L=4096, D=128, causal, FP8 QK): full-size launch, oracle
+    on 2 batches x 4 query heads; every output row is finite and non-zero."""
+    g = torch.Generator().manual_seed(SEED_ATTN)
+    B, L, Hq, Hkv = 4, 4096, 32, 8
+    q = torch.randn(B, L, Hq, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(B, L, Hkv, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(B, L, Hkv, 128, generator=g).bfloat16().cuda()
+    qq, sq = gk.quantize_rowwise(q, torch.float8_e4m3fn, transpose_scales=True)
+    kq, sk = gk.quantize_rowwise(k, torch.float8_e4m3fn, transpose_scales=True)
+    out = gk.triton_attn(qq, kq, v, sq, sk, causal=True)
+    assert bool(torch.isfinite(out.float()).all())
+    assert bool((out.float().abs().amax(-1) > 0).all())
+    for b, heads in ((0, [0, 5]), (3, [17, 31])):
+        for h in heads:
+            hk = h // 4
+            ref = oattn.attention_qk_quantized(u8(qq[b : b + 1, :, h : h + 1]), u8(kq[b : b + 1, :, hk : hk + 1]), v[b : b + 1, :, hk : hk + 1],
+                                               sq[b : b + 1, h : h + 1], sk[b : b + 1, hk : hk + 1], kind="e4m3", causal=True)
+            assert rel_err(out[b : b + 1, :, h : h + 1], ref) <= TOL
+
+
+def test_bad_arguments(gk):
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.int8, device="cuda")
+    with pytest.raises(NotImplementedError):
+        gk.triton_attn(q, q, q.bfloat16())
+    q = torch.zeros(1, 8, 2, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        gk.triton_attn(q, q, q)
