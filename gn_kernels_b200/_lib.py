@@ -42,6 +42,10 @@ _SIGNATURES = {
     "gnk_mm_nvfp4": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_float, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                              POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int, _P]),
+    "gnk_gemm_rs_flag_words": (c_int64, [c_int64, c_int64, c_int]),
+    "gnk_gemm_rs_plan": (c_int64, [c_int64, c_int64, c_int, c_int, c_int64, POINTER(c_int32)]),
+    "gnk_gemm_rs_bf16": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), POINTER(c_void_p), _P, c_int64, c_int64, c_int64,
+                                 c_int64, c_int, c_int, c_uint32, _P]),
     "gnk_debug_force_tile": (c_int, [c_int]),
     "gnk_debug_max_clusters": (c_int, [c_int]),
     "gnk_debug_trace": (c_int, [_P]),

@@ -1,0 +1,499 @@
+// tcgen05 GEMM kernel template shared by the single-GPU GEMM entry points and the fused
+// GEMM + reduce-scatter.  See gnk_gemm.cu for the description of the warp roles.
+#pragma once
+
+#include "gnk_common.cuh"
+
+namespace gnk {
+namespace gemm {
+
+enum Epi { EPI_BF16 = 0, EPI_ROWSCALED = 1, EPI_I32 = 2, EPI_RS = 3 };
+constexpr int kMaxWorld = 8;  // ranks of one NVLink domain the reduce-scatter variant addresses
+constexpr int kTraceEvents = 256;  // stages recorded per (CTA, role) when tracing
+
+template <MmaKind K> struct KindInfo;
+template <> struct KindInfo<MmaKind::F16> { static constexpr bool kBlockScaled = false; static constexpr int kSfPerStage = 0; };
+template <> struct KindInfo<MmaKind::I8> { static constexpr bool kBlockScaled = false; static constexpr int kSfPerStage = 0; };
+template <> struct KindInfo<MmaKind::F8F6F4> { static constexpr bool kBlockScaled = false; static constexpr int kSfPerStage = 0; };
+// scale bytes per operand row per K stage: 128 fp8 / 32 = 4, 256 fp4 / 16 = 16
+template <> struct KindInfo<MmaKind::MXF8F6F4> { static constexpr bool kBlockScaled = true; static constexpr int kSfPerStage = 4; };
+template <> struct KindInfo<MmaKind::MXF4NVF4> { static constexpr bool kBlockScaled = true; static constexpr int kSfPerStage = 16; };
+
+struct GemmArgs {
+  int M, N;
+  int k_iters;           // K stages of 128 bytes
+  int tiles_m, tiles_n;  // cluster tiles: (128 * CG) x BN
+  void* C;
+  int64_t ldc;
+  const float* scale_a;
+  const float* scale_b;
+  const float* bias;
+  float alpha;
+  int vec_ok;  // C rows 16-byte aligned: vector stores allowed
+  long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
+  // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
+  // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
+  // THIS GPU.  Flag words: one per owned 128 x BN unit, then a CTA ticket, then the exit counter.
+  struct {
+    int world, rank;
+    int rows_per_owner;    // M / world
+    int tiles_per_owner;   // cluster tiles along M per owner
+    unsigned int timeout_ms;
+    __nv_bfloat16* staging[kMaxWorld];
+    unsigned int* flags[kMaxWorld];
+    __nv_bfloat16* out;
+    int64_t ldo;
+  } rs;
+};
+
+template <MmaKind KIND, int BN, int CG>
+struct Cfg {
+  using KI = KindInfo<KIND>;
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = (BN / CG) * 128;
+  static constexpr int kSfAtomBytes = 128 * KI::kSfPerStage;           // one 128-row group, one stage
+  static constexpr int kSfaBytes = kSfAtomBytes;
+  static constexpr int kSfbGroups = BN >= 128 ? BN / 128 : 1;
+  static constexpr int kSfbBytes = kSfAtomBytes * kSfbGroups;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kSmemBudget = 227 * 1024 - 2048;                // barriers + alignment slack
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+  // TMEM columns
+  static constexpr int kSfaCols = KI::kSfPerStage;                      // 4 bytes per column, 128 rows -> 4 columns per 4 scales
+  static constexpr int kSfbCols = KI::kSfPerStage * kSfbGroups;
+  static constexpr int kSfCols = KI::kBlockScaled ? ((kSfaCols + kSfbCols + 15) / 16) * 16 : 0;
+  static constexpr bool kOverlap = 2 * BN + kSfCols > 512;
+  static constexpr int kAccStride = kOverlap ? (512 - kSfCols - BN) : BN;
+  static constexpr int kOverlapCols = BN - kAccStride;                  // 0 when the accumulators are disjoint
+  static constexpr int kSfBase = kOverlap ? 512 - kSfCols : 2 * BN;
+  static constexpr int kTmemCols = 512;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int kGroup = 8;
+  const int width = kGroup * tiles_n;
+  const int gid = t / width;
+  const int first = gid * kGroup;
+  const int gsz = min(tiles_m - first, kGroup);
+  const int in = t - gid * width;
+  tm = first + in % gsz;
+  tn = in / gsz;
+}
+
+// Reduce-scatter tile order.  Sequence index i -> owner (rank + 1 + i) % W, so that at any moment
+// every rank pushes to a different owner (each NVLink ingress sees one sender), and all ranks
+// produce local tile q = i / W of every owner within the same round of W tiles, which lets the
+// owners reduce right behind production.  Inside an owner, tn runs fastest (operand reuse in L2).
+__device__ __forceinline__ void tile_coords_rs(int i, const GemmArgs& g, int& tm, int& tn) {
+  const int owner = (g.rs.rank + 1 + i) % g.rs.world;
+  const int q = i / g.rs.world;
+  tn = q % g.tiles_n;
+  tm = owner * g.rs.tiles_per_owner + q / g.tiles_n;
+}
+template <int EPI>
+__device__ __forceinline__ void map_tile(int t, const GemmArgs& g, int& tm, int& tn) {
+  if constexpr (EPI == EPI_RS) tile_coords_rs(t, g, tm, tn);
+  else map_tile<EPI>(t, g, tm, tn);
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded poll of a flag word another GPU increments.  Returns false (and records `detail`) on give-up.
+__device__ __forceinline__ bool wait_flag_eq(const unsigned int* p, unsigned int want, unsigned int timeout_ms,
+                                             uint32_t detail) {
+  if (ld_acquire_sys(p) == want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t budget = static_cast<uint64_t>(timeout_ms) * 1000000ull;
+  while (ld_acquire_sys(p) != want) {
+    __nanosleep(64);
+    if (globaltimer_ns() - t0 > budget) {
+      report_timeout(detail);
+      return false;
+    }
+  }
+  return true;
+}
+
+// ---- epilogue: W (16 or 32) consecutive accumulator columns of one row ------------------
+template <MmaKind KIND, int EPI, int W>
+__device__ __forceinline__ void store_cols(const uint32_t* r, const GemmArgs& g, int row, int col0, float sa,
+                                           void* rowptr) {
+  if (row >= g.M || col0 >= g.N) return;
+  const bool full = (col0 + W <= g.N) && g.vec_ok;
+  if constexpr (EPI == EPI_I32) {
+    int32_t* dst = static_cast<int32_t*>(rowptr) + col0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < W; i += 4) *reinterpret_cast<uint4*>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+    } else {
+      for (int i = 0; i < W && col0 + i < g.N; ++i) dst[i] = static_cast<int32_t>(r[i]);
+    }
+  } else {
+    float f[W];
+#pragma unroll
+    for (int i = 0; i < W; ++i) {
+      float v = KIND == MmaKind::I8 ? static_cast<float>(static_cast<int32_t>(r[i])) : __uint_as_float(r[i]);
+      if constexpr (EPI == EPI_ROWSCALED) {
+        // order fixed by the reference epilogue: * scale_A[m], * scale_B[n], + bias[n], each rounded
+        const int c = min(col0 + i, g.N - 1);
+        if (g.scale_a) v = __fmul_rn(v, sa);
+        if (g.scale_b) v = __fmul_rn(v, __ldg(g.scale_b + c));
+        if (g.bias) v = __fadd_rn(v, __ldg(g.bias + c));
+      } else if constexpr (KIND == MmaKind::MXF4NVF4) {
+        v = __fmul_rn(v, g.alpha);
+      }
+      f[i] = v;
+    }
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(rowptr) + col0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < W; i += 8)
+        *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack_bf16x2(f[i], f[i + 1]), pack_bf16x2(f[i + 2], f[i + 3]),
+                                                        pack_bf16x2(f[i + 4], f[i + 5]), pack_bf16x2(f[i + 6], f[i + 7]));
+    } else {
+      for (int i = 0; i < W && col0 + i < g.N; ++i) dst[i] = __float2bfloat16_rn(f[i]);
+    }
+  }
+}
+
+// drains accumulator columns [c0, c1) (multiples of 16) of this warp's 32 rows
+template <MmaKind KIND, int EPI>
+__device__ __forceinline__ void drain_cols(uint32_t taddr_row, int c0, int c1, const GemmArgs& g, int row, int ncol0,
+                                           float sa, void* rowptr) {
+  int c = c0;
+  for (; c + 32 <= c1; c += 32) {
+    uint32_t r[32];
+    tmem_ld32(taddr_row + c, r);
+    tc_wait_ld();
+    store_cols<KIND, EPI, 32>(r, g, row, ncol0 + c, sa, rowptr);
+  }
+  for (; c + 16 <= c1; c += 16) {
+    uint32_t r[16];
+    tmem_ld16(taddr_row + c, r);
+    tc_wait_ld();
+    store_cols<KIND, EPI, 16>(r, g, row, ncol0 + c, sa, rowptr);
+  }
+}
+
+template <MmaKind KIND, int BN, int CG, int EPI>
+__global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+                const GemmArgs g) {
+  using C = Cfg<KIND, BN, CG>;
+  constexpr bool kBS = C::KI::kBlockScaled;
+  constexpr int S = C::kStages;
+  constexpr int kInner = KIND == MmaKind::F16 ? 64 : 128;  // tensor-map elements per 128-byte K stage
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // [stage][A | B | SFA | SFB]; A and B stage buffers stay 1024-byte aligned (sizes are multiples of 1024... SF after them)
+  auto stage_a = [&](int s) { return smem_base + s * (C::kABytes + C::kBBytes); };
+  auto stage_b = [&](int s) { return stage_a(s) + C::kABytes; };
+  const uint32_t sf_base = smem_base + S * (C::kABytes + C::kBBytes);
+  auto stage_sfa = [&](int s) { return sf_base + s * (C::kSfaBytes + C::kSfbBytes); };
+  auto stage_sfb = [&](int s) { return stage_sfa(s) + C::kSfaBytes; };
+  const uint32_t bar_base = sf_base + S * (C::kSfaBytes + C::kSfbBytes);
+  auto bar_full = [&](int s) { return bar_base + 8 * s; };
+  auto bar_empty = [&](int s) { return bar_base + 8 * (S + s); };
+  auto bar_tfull = [&](int s) { return bar_base + 8 * (2 * S + s); };
+  auto bar_tempty = [&](int s) { return bar_base + 8 * (2 * S + 2 + s); };
+  const uint32_t bar_partial = bar_base + 8 * (2 * S + 4);
+  const uint32_t tmem_slot = bar_base + 8 * (2 * S + 5);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int trace_it = 0;
+  const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / CG;
+  const int num_clusters = gridDim.x / CG;
+  const int num_tiles = g.tiles_m * g.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full(s), CG);  // one expect_tx arrival per CTA of the pair
+      mbar_init(bar_empty(s), 1);  // one tcgen05.commit
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull(s), 1);
+      mbar_init(bar_tempty(s), 4 * CG);  // one arrival per epilogue warp of every CTA
+    }
+    mbar_init(bar_partial, 4 * CG);
+    fence_mbar_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+    if constexpr (kBS) {
+      tma_prefetch_desc(&tm_sfa);
+      tma_prefetch_desc(&tm_sfb);
+    }
+  }
+  if (warp == 5) {
+    tmem_alloc<CG>(tmem_slot, C::kTmemCols);
+    tmem_relinquish<CG>();
+  }
+  tc_fence_before();
+  if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  // Producer and MMA warps run their loops warp-uniformly (all 32 lanes wait on the barriers and
+  // compute addresses and descriptors, which keeps those values in uniform registers); one
+  // elected lane executes the TMA / tcgen05 issue instructions.
+  if (warp == 4) {
+    // ------------------------------ producer ------------------------------
+    const bool leader = elect_one();
+    uint32_t stage = 0, parity = 1;
+    bool ok = true;
+    // both CTAs of a pair count their bytes on CTA 0's barrier
+    const uint32_t full0 = CG == 2 ? map_to_cta(bar_full(0), 0) : bar_full(0);
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int tm, tn;
+      map_tile<EPI>(t, g, tm, tn);
+      const int a_row = (tm * CG + cta_rank) * 128;
+      const int b_row = tn * BN + cta_rank * (BN / CG);
+      const int sfa_row = tm * CG + cta_rank;
+      const int sfb_row = (tn * BN) / 128;
+      for (int k = 0; k < g.k_iters; ++k) {
+        const long long tr0 = g.trace ? clock64() : 0;
+        if (!mbar_wait(bar_empty(stage), parity, (1u << 24) | (1u << 16) | stage)) { ok = false; break; }
+        const long long tr1 = g.trace ? clock64() : 0;
+        const uint32_t full = full0 + 8 * stage;
+        const uint32_t sa = stage_a(stage), sb = stage_b(stage);
+        if (leader) {
+          if constexpr (CG == 2) {
+            mbar_expect_tx_cluster(full, C::kStageBytes);
+            tma_load_2d_pair(sa, &tm_a, full, k * kInner, a_row);
+            tma_load_2d_pair(sb, &tm_b, full, k * kInner, b_row);
+            if constexpr (kBS) {
+              tma_load_2d_pair(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
+              tma_load_2d_pair(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), sfb_row);
+            }
+          } else {
+            mbar_expect_tx(full, C::kStageBytes);
+            tma_load_2d(sa, &tm_a, full, k * kInner, a_row);
+            tma_load_2d(sb, &tm_b, full, k * kInner, b_row);
+            if constexpr (kBS) {
+              tma_load_2d(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
+              tma_load_2d(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), sfb_row);
+            }
+          }
+          if (g.trace && blockIdx.x < 2 && trace_it < kTraceEvents) {
+            long long* tp = g.trace + ((blockIdx.x * 2 + 0) * kTraceEvents + trace_it) * 3;
+            tp[0] = tr0; tp[1] = tr1; tp[2] = clock64();
+          }
+        }
+        ++trace_it;
+        __syncwarp();
+        if (++stage == S) { stage = 0; parity ^= 1; }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (cta_rank == 0) {
+      const bool leader = elect_one();
+      uint32_t stage = 0, parity = 0, acc = 0, acc_parity = 1, iter = 0;
+      bool ok = true;
+      constexpr uint32_t kIdesc = KIND == MmaKind::F16      ? idesc_dense(1, 1, 1, 128 * CG, BN)
+                                  : KIND == MmaKind::I8     ? idesc_dense(2, 1, 1, 128 * CG, BN)
+                                  : KIND == MmaKind::F8F6F4 ? idesc_dense(1, 0, 0, 128 * CG, BN)
+                                  : KIND == MmaKind::MXF8F6F4 ? idesc_block_scaled(0, 1, 128 * CG, BN)
+                                                              : idesc_block_scaled(1, 0, 128 * CG, BN);
+      const uint32_t sf_tmem = tmem_base + C::kSfBase;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
+        if (!mbar_wait(bar_tempty(acc), acc_parity, (2u << 24) | (2u << 16) | acc)) { ok = false; break; }
+        if constexpr (C::kOverlap) {
+          if (iter > 0 && !mbar_wait(bar_partial, (iter - 1) & 1, (2u << 24) | (3u << 16))) { ok = false; break; }
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
+        for (int k = 0; k < g.k_iters; ++k) {
+          const long long tr0 = g.trace ? clock64() : 0;
+          if (!mbar_wait(bar_full(stage), parity, (2u << 24) | (4u << 16) | stage)) { ok = false; break; }
+          const long long tr1 = g.trace ? clock64() : 0;
+          tc_fence_after();
+          const uint64_t a_desc = sdesc_k128(stage_a(stage));
+          const uint64_t b_desc = sdesc_k128(stage_b(stage));
+          const uint64_t sfa_desc = sdesc_sf(stage_sfa(stage));
+          const uint64_t sfb_desc = sdesc_sf(stage_sfb(stage));
+          const uint32_t empty = bar_empty(stage);
+          if (leader) {
+            if constexpr (kBS) {
+              constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per stage: 1 (mxfp8) or 4 (nvfp4)
+#pragma unroll
+              for (int a = 0; a < kAtoms; ++a) {
+                tc_cp_sf<CG>(sf_tmem + 4 * a, sfa_desc + (512 >> 4) * a);
+#pragma unroll
+                for (int j = 0; j < C::kSfbGroups; ++j)
+                  tc_cp_sf<CG>(sf_tmem + C::kSfaCols + (a * C::kSfbGroups + j) * 4,
+                               sfb_desc + ((j * C::kSfAtomBytes + 512 * a) >> 4));
+              }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint32_t accum = (k | kk) != 0;
+              if constexpr (!kBS) {
+                tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, accum);
+              } else if constexpr (KIND == MmaKind::MXF8F6F4) {
+                // the four K steps of a stage read bytes 0..3 of the same scale columns (scale ids in the descriptor)
+                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc | (kk << 4) | (kk << 29), sf_tmem,
+                                    sf_tmem + C::kSfaCols, accum);
+              } else {
+                // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
+                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, sf_tmem + 4 * kk,
+                                    sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4, accum);
+              }
+            }
+            if constexpr (CG == 2) tc_commit_pair(empty, 3); else tc_commit<1>(empty);
+            if (g.trace && blockIdx.x < 2 && trace_it < kTraceEvents) {
+              long long* tp = g.trace + ((blockIdx.x * 2 + 1) * kTraceEvents + trace_it) * 3;
+              tp[0] = tr0; tp[1] = tr1; tp[2] = clock64();
+            }
+          }
+          ++trace_it;
+          __syncwarp();
+          if (++stage == S) { stage = 0; parity ^= 1; }
+        }
+        if (!ok) break;
+        if (leader) {
+          if constexpr (CG == 2) tc_commit_pair(bar_tfull(acc), 3); else tc_commit<1>(bar_tfull(acc));
+        }
+        __syncwarp();
+        acc ^= 1;
+        if (acc == 0) acc_parity ^= 1;
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------ epilogue (warps 0-3) ------------------------------
+    uint32_t acc = 0, parity = 0;
+    const uint32_t tempty0 = CG == 2 ? map_to_cta(bar_tempty(0), 0) : bar_tempty(0);
+    const uint32_t partial = CG == 2 ? map_to_cta(bar_partial, 0) : bar_partial;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int tm, tn;
+      map_tile<EPI>(t, g, tm, tn);
+      if (!mbar_wait(bar_tfull(acc), parity, (3u << 24) | (5u << 16) | acc)) { ok = false; break; }
+      tc_fence_after();
+      const int row = (tm * CG + cta_rank) * 128 + warp * 32 + lane;
+      const int ncol0 = tn * BN;
+      const float sa = (EPI == EPI_ROWSCALED && g.scale_a && row < g.M) ? __ldg(g.scale_a + row) : 1.f;
+      void* rowptr;
+      unsigned int* rs_flag = nullptr;
+      if constexpr (EPI == EPI_RS) {
+        // this rank's slot in the staging buffer of the rank that owns the row
+        const int owner = row / g.rs.rows_per_owner;
+        const int lrow = row - owner * g.rs.rows_per_owner;
+        rowptr = g.rs.staging[owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
+        const int lrow0 = (tm * CG + cta_rank) * 128 - owner * g.rs.rows_per_owner;
+        rs_flag = g.rs.flags[owner] + (lrow0 / 128) * g.tiles_n + tn;
+      } else if constexpr (EPI == EPI_I32) {
+        rowptr = static_cast<int32_t*>(g.C) + static_cast<int64_t>(row) * g.ldc;
+      } else {
+        rowptr = static_cast<__nv_bfloat16*>(g.C) + static_cast<int64_t>(row) * g.ldc;
+      }
+      const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + acc * C::kAccStride;
+      if constexpr (C::kOverlap) {
+        // the columns shared with the other accumulator go first and are released at once
+        const int o0 = acc == 0 ? C::kAccStride : 0;
+        const int o1 = o0 + C::kOverlapCols;
+        drain_cols<KIND, EPI>(taddr_row, o0, o1, g, row, ncol0, sa, rowptr);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(partial);
+        if (acc == 0) drain_cols<KIND, EPI>(taddr_row, 0, o0, g, row, ncol0, sa, rowptr);
+        else drain_cols<KIND, EPI>(taddr_row, o1, BN, g, row, ncol0, sa, rowptr);
+      } else {
+        drain_cols<KIND, EPI>(taddr_row, 0, BN, g, row, ncol0, sa, rowptr);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);
+      if constexpr (EPI == EPI_RS) {
+        // the tile is in the owner's memory once every thread's stores are ordered before the signal
+        __threadfence_system();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (threadIdx.x == 0) red_release_sys_add(rs_flag, 1u);
+      }
+      acc ^= 1;
+      if (acc == 0) parity ^= 1;
+    }
+  } else {
+    // ------------------------------ reducer (warps 6-9, reduce-scatter variant only) ------------------------------
+    if constexpr (EPI == EPI_RS) {
+      const int ct = threadIdx.x - 192;
+      const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;  // 128 x BN units this rank owns
+      unsigned int* my_flags = g.rs.flags[g.rs.rank];
+      const __nv_bfloat16* my_stage = g.rs.staging[g.rs.rank];
+      __shared__ int rs_ok;
+      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        if (ct == 0) rs_ok = wait_flag_eq(my_flags + u, g.rs.world, g.rs.timeout_ms, (4u << 24) | (6u << 16) | (u & 0xFFFF));
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        if (rs_ok) {
+          const int lr0 = (u / g.tiles_n) * 128, c0 = (u % g.tiles_n) * BN;
+          constexpr int kPiecesPerRow = BN / 8;
+          for (int piece = ct; piece < 128 * kPiecesPerRow; piece += 128) {
+            const int rr = lr0 + piece / kPiecesPerRow, cc = c0 + (piece % kPiecesPerRow) * 8;
+            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int sr = 0; sr < g.rs.world; ++sr) {
+              // L2-only loads: the lines were written by other GPUs during this kernel
+              const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
+                  my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr) * g.N + cc));
+              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                acc8[2 * e] += __uint_as_float(w[e] << 16);
+                acc8[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+              }
+            }
+            *reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr) * g.rs.ldo + cc) =
+                make_uint4(pack_bf16x2(acc8[0], acc8[1]), pack_bf16x2(acc8[2], acc8[3]), pack_bf16x2(acc8[4], acc8[5]),
+                           pack_bf16x2(acc8[6], acc8[7]));
+          }
+        }
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        if (ct == 0) my_flags[u] = 0u;  // ready for the next call (peers cannot signal again before the exit barrier)
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc<CG>(tmem_base, C::kTmemCols);
+  }
+  if constexpr (EPI == EPI_RS) {
+    // Exit barrier across ranks: a rank may start its next call (and overwrite staging slots on
+    // its peers) only after every peer has finished reducing this one.  The last CTA of this rank
+    // tells every peer, then waits (bounded) for the world - 1 peers to tell it.
+    if (CG == 1) __syncthreads();
+    if (threadIdx.x == 0) {
+      const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;
+      unsigned int* my_flags = g.rs.flags[g.rs.rank];
+      __threadfence();
+      const unsigned int ticket = atomicAdd(my_flags + units, 1u);
+      if (ticket == gridDim.x - 1) {
+        my_flags[units] = 0u;
+        __threadfence_system();
+        for (int p = 0; p < g.rs.world; ++p)
+          if (p != g.rs.rank) red_release_sys_add(g.rs.flags[p] + units + 1, 1u);
+        if (wait_flag_eq(my_flags + units + 1, g.rs.world - 1, g.rs.timeout_ms, (4u << 24) | (7u << 16)))
+          my_flags[units + 1] = 0u;
+      }
+    }
+  }
+}
+
+}  // namespace gemm
+}  // namespace gnk

@@ -1,0 +1,161 @@
+// BF16 GEMM fused with a reduce-scatter over NVLink peer memory (K sharded across ranks).
+//
+// Every rank computes its [M, N] partial tile by tile with the tcgen05 GEMM kernel; the epilogue
+// rounds a tile to bf16 and stores it straight into the staging slot (indexed by the sending
+// rank) of the rank that owns those rows, then bumps that owner's flag for the tile with a
+// system-scope release.  Four extra warps per CTA on the owner wait (bounded) until a tile's
+// flag shows all ranks, add the slots in fp32 from the owner's own HBM and write the bf16
+// output rows.  The kernel ends with a cross-rank exit barrier so that the next call cannot
+// overwrite staging that a slower rank is still reducing.  Only plain peer stores, peer
+// atomics and local loads cross or follow NVLink traffic: no TMA load here names peer memory
+// and none uses cluster multicast.
+#include "gnk_gemm_kernel.cuh"
+
+namespace gnk {
+namespace {
+
+using namespace gnk::gemm;
+
+GNK_DEFINE_STATUS_READER(gemm_rs_status_reader)
+
+struct RsPlan {
+  int cg, bn;
+  int tiles_m, tiles_n, tiles_per_owner, rows_per_owner, units;
+};
+
+int make_plan(int64_t M, int64_t N, int world, RsPlan* p) {
+  if (world < 1 || world > kMaxWorld || M <= 0 || N <= 0) return GNK_ERR_BAD_ARG;
+  if (M % world != 0) return GNK_ERR_BAD_SHAPE;
+  const int64_t rpo = M / world;
+  if (rpo % 256 == 0 && N % 256 == 0) {
+    p->cg = 2;
+    p->bn = 256;
+  } else if (rpo % 128 == 0 && N % 128 == 0) {
+    p->cg = 1;
+    p->bn = 128;
+  } else {
+    return GNK_ERR_BAD_SHAPE;
+  }
+  p->rows_per_owner = static_cast<int>(rpo);
+  p->tiles_m = static_cast<int>(M / (128 * p->cg));
+  p->tiles_n = static_cast<int>(N / p->bn);
+  p->tiles_per_owner = p->tiles_m / world;
+  p->units = static_cast<int>(rpo / 128) * p->tiles_n;
+  return GNK_OK;
+}
+
+template <int BN, int CG>
+int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g, int64_t M, int64_t N, int64_t K,
+              cudaStream_t st) {
+  using C = Cfg<MmaKind::F16, BN, CG>;
+  CUtensorMap tm_a, tm_b;
+  int rc = make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, M, K, ldx * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != GNK_OK) return rc;
+  rc = make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, w, N, K, ldw * 2, BN / CG, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != GNK_OK) return rc;
+  g.k_iters = static_cast<int>((K * 2 + 127) / 128);
+  auto kern = gemm_kernel<MmaKind::F16, BN, CG, EPI_RS>;
+  static int resident[64];
+  int dev = 0;
+  GNK_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return GNK_ERR_UNSUPPORTED;
+  if (resident[dev] == 0) {
+    GNK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    int n = num_sms() / CG;
+    if (CG > 1) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(num_sms() / CG * CG));
+      cfg.blockDim = dim3(320);
+      cfg.dynamicSmemBytes = C::kSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = CG;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int q = 0;
+      GNK_CUDA_OK(cudaOccupancyMaxActiveClusters(&q, kern, &cfg));
+      if (q > 0 && q < n) n = q;
+    }
+    resident[dev] = n;
+  }
+  int clusters = resident[dev];
+  const int tiles = g.tiles_m * g.tiles_n;
+  if (clusters > tiles) clusters = tiles;
+  kern<<<clusters * CG, 320, C::kSmemBytes, st>>>(tm_a, tm_b, tm_a, tm_b, g);
+  GNK_LAUNCH_OK();
+  return GNK_OK;
+}
+
+}  // namespace
+}  // namespace gnk
+
+using namespace gnk;
+
+extern "C" int64_t gnk_gemm_rs_flag_words(int64_t M, int64_t N, int world) {
+  RsPlan p;
+  if (make_plan(M, N, world, &p) != GNK_OK) return -1;
+  return p.units + 2;
+}
+
+// Host-side restatement of the device tile order, for tests: sequence index i -> the 128 x BN
+// units (owner, unit index) a cluster tile signals.  out[0..3] = {owner, tm, tn, first unit},
+// out[4] = units signalled by this tile (1 or 2).  Returns the number of cluster tiles.
+extern "C" int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, int64_t i, int32_t* out) {
+  RsPlan p;
+  if (make_plan(M, N, world, &p) != GNK_OK) return -1;
+  const int64_t total = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (out && i >= 0 && i < total) {
+    const int owner = static_cast<int>((rank + 1 + i) % world);
+    const int q = static_cast<int>(i / world);
+    const int tn = q % p.tiles_n;
+    const int tm = owner * p.tiles_per_owner + q / p.tiles_n;
+    const int lrow0 = tm * p.cg * 128 - owner * p.rows_per_owner;
+    out[0] = owner;
+    out[1] = tm;
+    out[2] = tn;
+    out[3] = (lrow0 / 128) * p.tiles_n + tn;
+    out[4] = p.cg;  // the second CTA of a pair signals unit out[3] + tiles_n
+  }
+  return total;
+}
+
+extern "C" int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
+                                int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
+                                int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream) {
+  if (!x || !w || !output || M <= 0 || N <= 0 || K_local <= 0) return GNK_ERR_BAD_ARG;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return GNK_ERR_BAD_ARG;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(output)) return GNK_ERR_BAD_ALIGN;
+  if (K_local % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldo % 8 != 0) return GNK_ERR_BAD_SHAPE;
+  int rc = check_arch();
+  if (rc != GNK_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (world == 1)  // nothing to exchange: the GEMM writes the output rows itself
+    return gnk_mm_bf16(x, ldx, w, ldw, output, ldo, M, N, K_local, stream);
+  if (!staging || !flags) return GNK_ERR_BAD_ARG;
+  RsPlan p;
+  rc = make_plan(M, N, world, &p);
+  if (rc != GNK_OK) return rc;
+  GemmArgs g{};
+  g.M = static_cast<int>(M);
+  g.N = static_cast<int>(N);
+  g.tiles_m = p.tiles_m;
+  g.tiles_n = p.tiles_n;
+  g.alpha = 1.f;
+  g.vec_ok = 1;
+  g.rs.world = world;
+  g.rs.rank = rank;
+  g.rs.rows_per_owner = p.rows_per_owner;
+  g.rs.tiles_per_owner = p.tiles_per_owner;
+  g.rs.timeout_ms = timeout_ms ? timeout_ms : 20000u;
+  for (int r = 0; r < world; ++r) {
+    if (!staging[r] || !flags[r] || !aligned16(staging[r])) return GNK_ERR_BAD_ARG;
+    g.rs.staging[r] = static_cast<__nv_bfloat16*>(staging[r]);
+    g.rs.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
+  }
+  g.rs.out = static_cast<__nv_bfloat16*>(output);
+  g.rs.ldo = ldo;
+  if (p.cg == 2) return launch_rs<256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
+  return launch_rs<128, 1>(x, ldx, w, ldw, g, M, N, K_local, st);
+}

@@ -1,0 +1,69 @@
+"""K-sharded BF16 GEMM fused with a reduce-scatter along M (one process per GPU).
+Upstream gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496; same call, same buffers
+(example_gemm_rs.py:14-26): `partial` is a symmetric-memory [M, N] bf16 buffer, `flags` a
+zero-initialised symmetric int32 buffer, both rendezvoused over the default group."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..._lib import check, lib
+
+
+def flag_words(M: int, N: int, world_size: int) -> int:
+    """int32 words `flags` must hold for this problem (never more than upstream's
+    (M/128)*(N/128) + SM-count allocation)."""
+    n = lib().gnk_gemm_rs_flag_words(M, N, world_size)
+    if n < 0:
+        raise ValueError(f"gemm_rs: unsupported shape M={M} N={N} world={world_size} (need M % (128*world) == 0, N % 128 == 0)")
+    return int(n)
+
+
+def gemm_rs(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    partial: torch.Tensor,
+    partial_handle,
+    output: torch.Tensor,
+    flags: torch.Tensor,
+    flags_handle,
+    *,
+    BN: int | None = None,
+    timeout_ms: int = 0,
+) -> torch.Tensor:
+    """output[M/W, N] = sum over ranks of bf16(x_r @ w_r^T)[this rank's rows], fp32 summation.
+
+    x [M, K/W], w [N, K/W] bf16 (this rank's K shard).  `partial` is used as staging: every rank
+    stores its bf16 tiles into the owner's buffer over NVLink, the owner reduces from its own
+    memory.  Device-side waits are bounded by `timeout_ms` (0 = 20 s); a wait that runs out is
+    reported by `gn_kernels_b200._lib.raise_on_device_error()`.  BN is accepted for upstream
+    compatibility; the tile shape is chosen from the problem shape."""
+    assert dist.is_initialized()
+    rank = dist.get_rank()
+    world = dist.get_world_size()
+    assert world <= 8
+    M, K = x.shape
+    N, _ = w.shape
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and output.dtype == torch.bfloat16
+    assert w.shape[1] == K and output.shape == (M // world, N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and output.stride(1) == 1
+    if world > 1:
+        assert partial.numel() >= M * N and partial.dtype == torch.bfloat16
+        assert flags.dtype == torch.int32 and flags.numel() >= flag_words(M, N, world)
+        sp = (ctypes.c_void_p * world)(*[int(p) for p in partial_handle.buffer_ptrs[:world]])
+        fp = (ctypes.c_void_p * world)(*[int(p) for p in flags_handle.buffer_ptrs[:world]])
+    else:
+        sp = fp = None
+    stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    with torch.cuda.device(x.device):
+        check(
+            lib().gnk_gemm_rs_bf16(
+                ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(w.data_ptr()), w.stride(0), sp, fp,
+                ctypes.c_void_p(output.data_ptr()), output.stride(0), M, N, K, rank, world, timeout_ms, stream,
+            ),
+            "gnk_gemm_rs_bf16",
+        )
+    return output

@@ -169,21 +169,36 @@ int gnk_attn_fwd(const void* q, const void* k, const void* v, void* o, const flo
 
 /* ------------------------------------------------------------------ GEMM + RS ----- */
 
-/* Number of int32 words the flags buffer of gnk_gemm_rs_bf16 must hold. */
+/* Number of int32 words the flags buffer of gnk_gemm_rs_bf16 must hold (-1 for a shape the op rejects). */
 int64_t gnk_gemm_rs_flag_words(int64_t M, int64_t N, int world);
+
+/* Host-side restatement of the device tile order (for tests of the ownership / flag arithmetic):
+ * for sequence index i of `rank`, out[0..4] = {owner rank, tile row, tile column, first flag word
+ * signalled, number of 128-row units signalled}.  Returns the number of tiles, -1 for a bad shape. */
+int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, int64_t i, int32_t* out);
 
 /* K-sharded bf16 GEMM fused with a reduce-scatter along M over NVLink peer memory.
  * x [M, K_local], w [N, K_local] (this rank's K shard).  staging[r] / flags[r]: device
- * pointers, valid on THIS GPU, to rank r's staging buffer (world * (M/world) * N bf16) and
- * flag words (zero before the first call; the kernel leaves them zero).  Every rank writes
- * each finished tile into the owner's staging slot for this rank and bumps the owner's
- * flag; the owner sums the `world` slots from its own memory in fp32 and writes
- * output [M/world, N] bf16.  All device-side waits are bounded (GNK_ERR_TIMEOUT through
- * gnk_device_status).  M % (128*world) == 0, N % 128 == 0, K_local % 8 == 0.
+ * pointers, valid on THIS GPU, to rank r's staging buffer (M * N bf16: `world` slots of
+ * [M/world, N]) and flag words (zero before the first call; the kernel leaves them zero).
+ * Every rank stores each finished bf16 tile into the owner's staging slot for this rank and
+ * bumps the owner's flag; the owner sums the `world` slots from its own memory in fp32 and
+ * writes output [M/world, N] bf16; an exit barrier across ranks ends the call.  All
+ * device-side waits are bounded by timeout_ms (0 = 20 s; GNK_ERR_TIMEOUT through
+ * gnk_device_status).  M % (128*world) == 0, N % 128 == 0, K_local % 8 == 0, world <= 8.
+ * world == 1 degenerates to gnk_mm_bf16 into `output`.
  * Replaces: gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496 `gemm_rs`. */
 int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
                      int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
-                     int64_t K_local, int rank, int world, uint32_t epoch, gnk_stream_t stream);
+                     int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream);
+
+/* ------------------------------------------------------------------ test hooks ---- */
+/* Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, -1: automatic),
+ * cap the persistent grid (0 = no cap), record per-stage clock stamps of CTAs 0 and 1 into a device
+ * buffer of 2*2*256*3 int64 (NULL = off).  Process-wide; for tests and profiling only. */
+int gnk_debug_force_tile(int sel);
+int gnk_debug_max_clusters(int n);
+int gnk_debug_trace(void* device_buffer);
 
 #ifdef __cplusplus
 }

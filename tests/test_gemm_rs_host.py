@@ -1,0 +1,94 @@
+"""CPU tests of the reduce-scatter host logic: tile order / ownership / flag accounting (through the
+C ABI's planning helper, no GPU work) and the sharding semantics on 2 gloo ranks."""
+
+import ctypes
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _plan(L, M, N, W, rank):
+    out = (ctypes.c_int32 * 5)()
+    total = L.gnk_gemm_rs_plan(M, N, W, rank, 0, out)
+    rows = []
+    for i in range(total):
+        L.gnk_gemm_rs_plan(M, N, W, rank, i, out)
+        rows.append(tuple(out))
+    return total, rows
+
+
+@pytest.mark.parametrize("M,N,W", [(8192, 8192, 8), (2048, 7168, 4), (512, 256, 2), (384, 384, 3), (1024, 512, 1)])
+def test_tile_order_covers_everything_once_and_spreads_owners(M, N, W):
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    words = L.gnk_gemm_rs_flag_words(M, N, W)
+    assert words > 0
+    signals = {}
+    for rank in range(W):
+        total, rows = _plan(L, M, N, W, rank)
+        seen = set()
+        for i, (owner, tm, tn, unit, nunits) in enumerate(rows):
+            assert (tm, tn) not in seen
+            seen.add((tm, tn))
+            assert 0 <= owner < W and 0 <= unit and unit + (nunits - 1) * (N // (256 if nunits == 2 else 128)) < words - 2
+            # at every step the ranks target pairwise different owners
+            assert owner == (rank + 1 + i) % W
+            for k in range(nunits):
+                key = (owner, unit + k * (N // 256 if nunits == 2 else 0))
+                signals[key] = signals.get(key, 0) + 1
+        assert len(seen) == total
+    # every owned unit is signalled exactly once by every rank
+    assert set(signals.values()) == {W}
+    assert len(signals) == W * (words - 2)
+
+
+def test_bad_shapes_rejected():
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    assert L.gnk_gemm_rs_flag_words(1000, 256, 8) == -1
+    assert L.gnk_gemm_rs_flag_words(1024, 200, 8) == -1
+    assert L.gnk_gemm_rs_flag_words(1024, 256, 9) == -1
+
+
+def _gloo_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    from oracle import gemm_rs as ors
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    M, N, Kl = 256, 128, 64
+    g = torch.Generator().manual_seed(1234 + rank)
+    x = torch.randn(M, Kl, generator=g).bfloat16()
+    w = torch.randn(N, Kl, generator=g).bfloat16()
+    # what the kernel does, spelled with collectives: bf16 partial, push row blocks to their owners, fp32 sum
+    partial = (x.float() @ w.float().T).bfloat16()
+    rows = M // world
+    parts = [torch.empty_like(partial) for _ in range(world)]
+    dist.all_gather(parts, partial)  # gloo has no all_to_all: gather, then keep the rows this rank owns
+    mine = sum(t[rank * rows : (rank + 1) * rows].float() for t in parts).bfloat16()
+    xs = [torch.empty_like(x) for _ in range(world)]
+    ws = [torch.empty_like(w) for _ in range(world)]
+    dist.all_gather(xs, x)
+    dist.all_gather(ws, w)
+    ref = ors.gemm_rs(xs, ws)[rank]
+    q.put((rank, bool(torch.equal(mine, ref))))
+    dist.destroy_process_group()
+
+
+def test_sharding_semantics_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, 2, 29541, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(0, True), (1, True)]
