@@ -42,6 +42,7 @@ _SIGNATURES = {
     "gnk_mm_nvfp4": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_float, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                              POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int, _P]),
+    "gnk_mm_f8_block128": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, _P, c_int64, _P, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_gemm_rs_flag_words": (c_int64, [c_int64, c_int64, c_int]),
     "gnk_gemm_rs_plan": (c_int64, [c_int64, c_int64, c_int, c_int, c_int64, POINTER(c_int32)]),
     "gnk_gemm_rs_bf16": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), POINTER(c_void_p), _P, c_int64, c_int64, c_int64,

@@ -85,12 +85,26 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // Reduce-scatter tile order.  Sequence index i -> owner (rank + 1 + i) % W, so that at any moment
 // every rank pushes to a different owner (each NVLink ingress sees one sender), and all ranks
 // produce local tile q = i / W of every owner within the same round of W tiles, which lets the
-// owners reduce right behind production.  Inside an owner, tn runs fastest (operand reuse in L2).
+// owners reduce right behind production.
+__host__ __device__ __forceinline__ void rs_local_tile(int q, int tiles_per_owner, int tiles_n, int world, int& lm,
+                                                        int& tn) {
+  // inside an owner: groups of up to 8 / world tile rows, tile row fastest inside a group, so that a
+  // wave of concurrently running tiles (all owners together) touches ~8 row blocks and ~9 column blocks
+  int grp_rows = 8 / world;
+  if (grp_rows < 1) grp_rows = 1;
+  if (grp_rows > tiles_per_owner) grp_rows = tiles_per_owner;
+  const int per = grp_rows * tiles_n;
+  const int grp = q / per, rem = q - grp * per;
+  const int first = grp * grp_rows;
+  const int gsz = tiles_per_owner - first < grp_rows ? tiles_per_owner - first : grp_rows;
+  lm = first + rem % gsz;
+  tn = rem / gsz;
+}
 __device__ __forceinline__ void tile_coords_rs(int i, const GemmArgs& g, int& tm, int& tn) {
   const int owner = (g.rs.rank + 1 + i) % g.rs.world;
-  const int q = i / g.rs.world;
-  tn = q % g.tiles_n;
-  tm = owner * g.rs.tiles_per_owner + q / g.tiles_n;
+  int lm;
+  rs_local_tile(i / g.rs.world, g.rs.tiles_per_owner, g.tiles_n, g.rs.world, lm, tn);
+  tm = owner * g.rs.tiles_per_owner + lm;
 }
 template <int EPI>
 __device__ __forceinline__ void map_tile(int t, const GemmArgs& g, int& tm, int& tn) {
@@ -441,23 +455,41 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         if (rs_ok) {
           const int lr0 = (u / g.tiles_n) * 128, c0 = (u % g.tiles_n) * BN;
           constexpr int kPiecesPerRow = BN / 8;
-          for (int piece = ct; piece < 128 * kPiecesPerRow; piece += 128) {
-            const int rr = lr0 + piece / kPiecesPerRow, cc = c0 + (piece % kPiecesPerRow) * 8;
-            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int sr = 0; sr < g.rs.world; ++sr) {
-              // L2-only loads: the lines were written by other GPUs during this kernel
-              const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
-                  my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr) * g.N + cc));
-              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread: kUnroll x world
+          for (int p0 = ct; p0 < 128 * kPiecesPerRow; p0 += 128 * kUnroll) {
+            float acc8[kUnroll][8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                acc8[2 * e] += __uint_as_float(w[e] << 16);
-                acc8[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+            for (int q = 0; q < kUnroll; ++q)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc8[q][e] = 0.f;
+            for (int sr = 0; sr < g.rs.world; ++sr) {
+              uint4 v[kUnroll];
+#pragma unroll
+              for (int q = 0; q < kUnroll; ++q) {
+                const int piece = p0 + q * 128;
+                const int rr = lr0 + piece / kPiecesPerRow, cc = c0 + (piece % kPiecesPerRow) * 8;
+                // L2-only loads: the lines were written by other GPUs during this kernel
+                v[q] = __ldcg(reinterpret_cast<const uint4*>(
+                    my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr) * g.N + cc));
+              }
+#pragma unroll
+              for (int q = 0; q < kUnroll; ++q) {
+                const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  acc8[q][2 * e] += __uint_as_float(w[e] << 16);
+                  acc8[q][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+                }
               }
             }
-            *reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr) * g.rs.ldo + cc) =
-                make_uint4(pack_bf16x2(acc8[0], acc8[1]), pack_bf16x2(acc8[2], acc8[3]), pack_bf16x2(acc8[4], acc8[5]),
-                           pack_bf16x2(acc8[6], acc8[7]));
+#pragma unroll
+            for (int q = 0; q < kUnroll; ++q) {
+              const int piece = p0 + q * 128;
+              const int rr = lr0 + piece / kPiecesPerRow, cc = c0 + (piece % kPiecesPerRow) * 8;
+              *reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr) * g.rs.ldo + cc) =
+                  make_uint4(pack_bf16x2(acc8[q][0], acc8[q][1]), pack_bf16x2(acc8[q][2], acc8[q][3]),
+                             pack_bf16x2(acc8[q][4], acc8[q][5]), pack_bf16x2(acc8[q][6], acc8[q][7]));
+            }
           }
         }
         asm volatile("bar.sync 3, 128;" ::: "memory");
@@ -477,7 +509,6 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     // Exit barrier across ranks: a rank may start its next call (and overwrite staging slots on
     // its peers) only after every peer has finished reducing this one.  The last CTA of this rank
     // tells every peer, then waits (bounded) for the world - 1 peers to tell it.
-    if (CG == 1) __syncthreads();
     if (threadIdx.x == 0) {
       const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;
       unsigned int* my_flags = g.rs.flags[g.rs.rank];

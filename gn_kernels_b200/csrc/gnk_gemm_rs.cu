@@ -108,9 +108,9 @@ extern "C" int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, i
   const int64_t total = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (out && i >= 0 && i < total) {
     const int owner = static_cast<int>((rank + 1 + i) % world);
-    const int q = static_cast<int>(i / world);
-    const int tn = q % p.tiles_n;
-    const int tm = owner * p.tiles_per_owner + q / p.tiles_n;
+    int lm, tn;
+    rs_local_tile(static_cast<int>(i / world), p.tiles_per_owner, p.tiles_n, world, lm, tn);
+    const int tm = owner * p.tiles_per_owner + lm;
     const int lrow0 = tm * p.cg * 128 - owner * p.rows_per_owner;
     out[0] = owner;
     out[1] = tm;

@@ -1,0 +1,1 @@
+from . import sm120_mm_fp8_1d2d  # noqa: F401

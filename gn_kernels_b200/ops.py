@@ -355,3 +355,33 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, scale_q: Tensor | None, scale_k: T
 def _(q, k, v, scale_q, scale_k, causal):
     B, Lq, Hq, D = q.shape
     return q.new_empty((B, Lq, Hq, D), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("gnk::mm_f8_block128", mutates_args=())
+def mm_f8_block128(A: Tensor, SFA: Tensor, Bt: Tensor, SFB: Tensor, bias: Tensor | None, add: Tensor | None) -> Tensor:
+    _need_cuda(A, Bt, SFA, SFB)
+    M, K = A.shape
+    N = Bt.shape[0]
+    A, Bt = _k_major(A), _k_major(Bt)
+    # SFA M-major: element (m, kb) at kb * ld + m
+    sfa = SFA.to(torch.float32)
+    if not (sfa.stride(0) == 1 and sfa.stride(1) >= M):
+        sfa = sfa.T.contiguous().T
+    sfb = SFB.to(torch.float32).contiguous()
+    bi = bias.to(torch.bfloat16).contiguous() if bias is not None else None
+    ad = add.to(torch.bfloat16) if add is not None else None
+    if ad is not None and ad.stride(1) != 1:
+        ad = ad.contiguous()
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    with torch.cuda.device(A.device):
+        check(
+            lib().gnk_mm_f8_block128(_p(A), A.stride(0), _p(sfa), sfa.stride(1) if sfa.shape[1] > 1 else max(M, 1), _p(Bt), Bt.stride(0), _p(sfb), sfb.stride(0),
+                                     _p(bi), _p(ad), ad.stride(0) if ad is not None else 0, _p(C), N, M, N, K, _stream(A)),
+            "gnk_mm_f8_block128",
+        )
+    return C
+
+
+@mm_f8_block128.register_fake
+def _(A, SFA, Bt, SFB, bias, add):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)

@@ -71,6 +71,7 @@ def main():
                 print(f"gemm_rs W={W} M={M} N={N} K={Kl * W} call {it}: max rel err {max(errs):.2e} bit-equal-to-oracle={exact} {'OK' if ok else 'FAIL'}", flush=True)
                 failures += 0 if ok else 1
             assert int(flags.abs().sum()) == 0, "flags not restored to zero"
+            dist.barrier()  # a faster peer's next call may signal this rank's flags as soon as it starts
         dist.barrier()
 
     if args.bench:

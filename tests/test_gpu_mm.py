@@ -254,3 +254,29 @@ def test_bad_arguments(gk):
         gk.triton_mm(A.half(), A.half().T)
     with pytest.raises(RuntimeError):
         gk.triton_mm(A.cpu(), A.cpu().T)
+
+
+def test_fp8_block128_golden(gk, golden_mm):
+    g = golden_mm
+    A = torch.from_numpy(g["blk_A"]).view(torch.float8_e4m3fn).cuda()
+    Bt = torch.from_numpy(g["blk_Bt"]).view(torch.float8_e4m3fn).cuda()
+    sfa = torch.from_numpy(g["blk_sfa"]).cuda()
+    sfb = torch.from_numpy(g["blk_sfb"]).cuda()
+    out = gk.cutedsl.sm120.sm120_mm_fp8_1d2d.mm(A, sfa.T.contiguous().T, Bt, sfb)  # SFA stored M-major as upstream wants
+    assert rel_err(out, bf16_from_bits(g["blk_ref"])) <= TOL
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (200, 256, 512), (1, 128, 1024), (1024, 1536, 7168 // 4)])
+@pytest.mark.parametrize("extras", [False, True])
+def test_fp8_block128(gk, M, N, K, extras):
+    g = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    Bt = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    sfa = (torch.rand(K // 128, M, generator=g) + 0.25).T  # M-major view [M, K/128]
+    sfb = torch.rand(N // 128, K // 128, generator=g) + 0.25
+    bias = torch.randn(N, generator=g).bfloat16() if extras else None
+    add = torch.randn(M, N, generator=g).bfloat16() if extras else None
+    out = gk.cutedsl.sm120.sm120_mm_fp8_1d2d.mm(A.cuda(), sfa.cuda(), Bt.cuda(), sfb.cuda(),
+                                                bias.cuda() if extras else None, add.cuda() if extras else None)
+    ref = omm.mm_f8_block128(u8(A), sfa, u8(Bt), sfb, bias, add)
+    assert rel_err(out, ref) <= TOL
