@@ -1,0 +1,62 @@
+"""CPU checks of the drop-in boundary: the shared library loads without a GPU and exports every
+function include/gnk.h declares; argument validation refuses bad calls before any CUDA work."""
+
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "gnk.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gnk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    names = declared_functions()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in gnk.h but not exported by libgnk.so"
+    # and the Python binding table covers them
+    for n in names:
+        assert n in _lib._SIGNATURES, f"{n} has no ctypes signature"
+
+
+def test_version_and_error_text():
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    assert L.gnk_version() == 100
+    assert L.gnk_strerror(0) == b"ok"
+    assert b"align" in L.gnk_strerror(-3)
+
+
+def test_bad_arguments_are_refused_without_a_gpu():
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    null = ctypes.c_void_p(0)
+    assert L.gnk_mm_mxfp8(null, 0, null, 0, null, null, null, 0, 128, 128, 128, null) == _lib.ERR_BAD_ARG
+    assert L.gnk_quant_nvfp4(null, 0, 1, 16, 16, null, 1e-12, null, null, 0, null) == _lib.ERR_BAD_ARG
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.c_void_p(ctypes.addressof(buf) // 16 * 16 + 16)
+    assert L.gnk_quant_mx(p, 0, 4, 33, 40, 1, 0, p, p, 0, null) == _lib.ERR_BAD_SHAPE
+    assert L.gnk_quant_rowwise(p, 0, 4, 12, 16, 0, p, p, 0, 0, null) == _lib.ERR_BAD_SHAPE
+    assert L.gnk_gemm_rs_flag_words(1000, 256, 8) == -1
+
+
+def test_cpu_tensors_raise():
+    import pytest
+    import torch
+
+    import gn_kernels_b200 as gk
+
+    with pytest.raises(RuntimeError):
+        gk.quantize_nvfp4(torch.randn(16, 64).bfloat16())
+    with pytest.raises(RuntimeError):
+        gk.triton_mm(torch.zeros(16, 16, dtype=torch.int8), torch.zeros(16, 16, dtype=torch.int8))
