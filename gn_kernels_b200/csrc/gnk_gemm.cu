@@ -38,7 +38,7 @@ struct ElemInfo {
 template <MmaKind KIND, int BN, int CG, int EPI>
 int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA, const uint8_t* SFB,
            GemmArgs g, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
-  using C = Cfg<KIND, BN, CG>;
+  using C = Cfg<KIND, BN, CG, EPI>;
   using EI = ElemInfo<KIND>;
   const int64_t k_bytes = K * EI::kNum / EI::kDen;
   const int64_t lda_b = lda * EI::kNum;  // ld counts stored elements (bytes for packed fp4)

@@ -46,9 +46,13 @@ struct GemmArgs {
   } rs;
 };
 
-template <MmaKind KIND, int BN, int CG>
+template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16>
 struct Cfg {
   using KI = KindInfo<KIND>;
+  // bf16 outputs of the 256-wide pair tile leave through a per-warp shared-memory staging area
+  // (32 rows x BN) so that every global store instruction writes one whole 512-byte row segment
+  static constexpr bool kStaged = BN == 256 && CG == 2 && EPI != EPI_I32;
+  static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : 0;
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = (BN / CG) * 128;
   static constexpr int kSfAtomBytes = 128 * KI::kSfPerStage;           // one 128-row group, one stage
@@ -56,10 +60,10 @@ struct Cfg {
   static constexpr int kSfbGroups = BN >= 128 ? BN / 128 : 1;
   static constexpr int kSfbBytes = kSfAtomBytes * kSfbGroups;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBudget = 227 * 1024 - 2048;                // barriers + alignment slack
+  static constexpr int kSmemBudget = 227 * 1024 - 2048 - kEpiBytes;    // barriers + alignment slack
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2048 + kEpiBytes;
   // TMEM columns
   static constexpr int kSfaCols = KI::kSfPerStage;                      // 4 bytes per column, 128 rows -> 4 columns per 4 scales
   static constexpr int kSfbCols = KI::kSfPerStage * kSfbGroups;
@@ -109,7 +113,7 @@ __device__ __forceinline__ void tile_coords_rs(int i, const GemmArgs& g, int& tm
 template <int EPI>
 __device__ __forceinline__ void map_tile(int t, const GemmArgs& g, int& tm, int& tn) {
   if constexpr (EPI == EPI_RS) tile_coords_rs(t, g, tm, tn);
-  else map_tile<EPI>(t, g, tm, tn);
+  else tile_coords(t, g.tiles_m, g.tiles_n, tm, tn);
 }
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -136,6 +140,24 @@ __device__ __forceinline__ bool wait_flag_eq(const unsigned int* p, unsigned int
   return true;
 }
 
+// fp32/int32 accumulator values of W consecutive columns -> finished fp32 values (epilogue math)
+template <MmaKind KIND, int EPI, int W>
+__device__ __forceinline__ void finish_cols(const uint32_t* r, const GemmArgs& g, int col0, float sa, float* f) {
+#pragma unroll
+  for (int i = 0; i < W; ++i) {
+    float v = KIND == MmaKind::I8 ? static_cast<float>(static_cast<int32_t>(r[i])) : __uint_as_float(r[i]);
+    if constexpr (EPI == EPI_ROWSCALED) {
+      const int c = min(col0 + i, g.N - 1);
+      if (g.scale_a) v = __fmul_rn(v, sa);
+      if (g.scale_b) v = __fmul_rn(v, __ldg(g.scale_b + c));
+      if (g.bias) v = __fadd_rn(v, __ldg(g.bias + c));
+    } else if constexpr (KIND == MmaKind::MXF4NVF4) {
+      v = __fmul_rn(v, g.alpha);
+    }
+    f[i] = v;
+  }
+}
+
 // ---- epilogue: W (16 or 32) consecutive accumulator columns of one row ------------------
 template <MmaKind KIND, int EPI, int W>
 __device__ __forceinline__ void store_cols(const uint32_t* r, const GemmArgs& g, int row, int col0, float sa,
@@ -152,20 +174,7 @@ __device__ __forceinline__ void store_cols(const uint32_t* r, const GemmArgs& g,
     }
   } else {
     float f[W];
-#pragma unroll
-    for (int i = 0; i < W; ++i) {
-      float v = KIND == MmaKind::I8 ? static_cast<float>(static_cast<int32_t>(r[i])) : __uint_as_float(r[i]);
-      if constexpr (EPI == EPI_ROWSCALED) {
-        // order fixed by the reference epilogue: * scale_A[m], * scale_B[n], + bias[n], each rounded
-        const int c = min(col0 + i, g.N - 1);
-        if (g.scale_a) v = __fmul_rn(v, sa);
-        if (g.scale_b) v = __fmul_rn(v, __ldg(g.scale_b + c));
-        if (g.bias) v = __fadd_rn(v, __ldg(g.bias + c));
-      } else if constexpr (KIND == MmaKind::MXF4NVF4) {
-        v = __fmul_rn(v, g.alpha);
-      }
-      f[i] = v;
-    }
+    finish_cols<KIND, EPI, W>(r, g, col0, sa, f);
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(rowptr) + col0;
     if (full) {
 #pragma unroll
@@ -197,12 +206,50 @@ __device__ __forceinline__ void drain_cols(uint32_t taddr_row, int c0, int c1, c
   }
 }
 
+// Staged epilogue, step 1: columns [c0, c1) of this thread's row -> bf16 -> the warp's staging
+// area (row pitch BN*2 bytes; the 16-byte column index is XORed with the row so that both this
+// write and the row-wise read back are bank-conflict free).
+template <MmaKind KIND, int EPI, int BN>
+__device__ __forceinline__ void drain_to_smem(uint32_t taddr_row, int c0, int c1, const GemmArgs& g, int ncol0, float sa,
+                                              uint32_t stg, int r) {
+  for (int c = c0; c < c1; c += 16) {
+    uint32_t raw[16];
+    tmem_ld16(taddr_row + c, raw);
+    tc_wait_ld();
+    float f[16];
+    finish_cols<KIND, EPI, 16>(raw, g, ncol0 + c, sa, f);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t addr = stg + r * (BN * 2) + ((((c >> 3) + j) ^ r) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(f[8 * j], f[8 * j + 1])),
+                   "r"(pack_bf16x2(f[8 * j + 2], f[8 * j + 3])), "r"(pack_bf16x2(f[8 * j + 4], f[8 * j + 5])),
+                   "r"(pack_bf16x2(f[8 * j + 6], f[8 * j + 7]))
+                   : "memory");
+    }
+  }
+}
+// Staged epilogue, step 2: the warp writes its 32 rows, one full row (BN bf16 = 32 lanes x 16 bytes) per instruction.
+template <int BN>
+__device__ __forceinline__ void flush_smem_rows(uint32_t stg, int lane, __nv_bfloat16* row0_ptr, int64_t row_pitch,
+                                                int rows_valid) {
+  static_assert(BN == 256, "one 16-byte piece per lane");
+#pragma unroll 4
+  for (int rr = 0; rr < 32; ++rr) {
+    uint32_t a, b, c, d;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                 : "r"(stg + rr * (BN * 2) + ((lane ^ rr) << 4))
+                 : "memory");
+    if (rr < rows_valid) *reinterpret_cast<uint4*>(row0_ptr + rr * row_pitch + lane * 8) = make_uint4(a, b, c, d);
+  }
+}
+
 template <MmaKind KIND, int BN, int CG, int EPI>
 __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                 const GemmArgs g) {
-  using C = Cfg<KIND, BN, CG>;
+  using C = Cfg<KIND, BN, CG, EPI>;
   constexpr bool kBS = C::KI::kBlockScaled;
   constexpr int S = C::kStages;
   constexpr int kInner = KIND == MmaKind::F16 ? 64 : 128;  // tensor-map elements per 128-byte K stage
@@ -222,6 +269,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   auto bar_tempty = [&](int s) { return bar_base + 8 * (2 * S + 2 + s); };
   const uint32_t bar_partial = bar_base + 8 * (2 * S + 4);
   const uint32_t tmem_slot = bar_base + 8 * (2 * S + 5);
+  const uint32_t epi_smem = (tmem_slot + 8 + 127u) & ~127u;  // staging area of the staged epilogue (if any)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -416,22 +464,41 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         rowptr = static_cast<__nv_bfloat16*>(g.C) + static_cast<int64_t>(row) * g.ldc;
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + acc * C::kAccStride;
+      // staged path: full tiles with 16-byte aligned rows (always the case for the reduce-scatter variant)
+      bool staged = false;
+      if constexpr (C::kStaged) staged = g.vec_ok && (ncol0 + BN <= g.N);
+      const uint32_t stg = epi_smem + warp * (32 * BN * 2);
       if constexpr (C::kOverlap) {
         // the columns shared with the other accumulator go first and are released at once
         const int o0 = acc == 0 ? C::kAccStride : 0;
         const int o1 = o0 + C::kOverlapCols;
-        drain_cols<KIND, EPI>(taddr_row, o0, o1, g, row, ncol0, sa, rowptr);
+        if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, o0, o1, g, ncol0, sa, stg, lane);
+        else drain_cols<KIND, EPI>(taddr_row, o0, o1, g, row, ncol0, sa, rowptr);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(partial);
-        if (acc == 0) drain_cols<KIND, EPI>(taddr_row, 0, o0, g, row, ncol0, sa, rowptr);
-        else drain_cols<KIND, EPI>(taddr_row, o1, BN, g, row, ncol0, sa, rowptr);
+        const int p0 = acc == 0 ? 0 : o1, p1 = acc == 0 ? o0 : BN;
+        if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, p0, p1, g, ncol0, sa, stg, lane);
+        else drain_cols<KIND, EPI>(taddr_row, p0, p1, g, row, ncol0, sa, rowptr);
       } else {
-        drain_cols<KIND, EPI>(taddr_row, 0, BN, g, row, ncol0, sa, rowptr);
+        if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
+        else drain_cols<KIND, EPI>(taddr_row, 0, BN, g, row, ncol0, sa, rowptr);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);
+      if constexpr (C::kStaged) {
+        if (staged) {
+          // TMEM is already released; now the warp streams its 32 rows out, 512 contiguous bytes per instruction
+          const int wrow0 = (tm * CG + cta_rank) * 128 + warp * 32;
+          // lane 0 holds the pointer of the warp's first row; the rows follow at a fixed pitch
+          __nv_bfloat16* first =
+              reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(rowptr), 0)) + ncol0;
+          const int64_t pitch = EPI == EPI_RS ? static_cast<int64_t>(g.N) : g.ldc;
+          flush_smem_rows<BN>(stg, lane, first, pitch, min(32, g.M - wrow0));
+          __syncwarp();
+        }
+      }
       if constexpr (EPI == EPI_RS) {
         // the tile is in the owner's memory once every thread's stores are ordered before the signal
         __threadfence_system();

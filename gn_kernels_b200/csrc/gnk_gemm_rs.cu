@@ -47,7 +47,7 @@ int make_plan(int64_t M, int64_t N, int world, RsPlan* p) {
 template <int BN, int CG>
 int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g, int64_t M, int64_t N, int64_t K,
               cudaStream_t st) {
-  using C = Cfg<MmaKind::F16, BN, CG>;
+  using C = Cfg<MmaKind::F16, BN, CG, EPI_RS>;
   CUtensorMap tm_a, tm_b;
   int rc = make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, M, K, ldx * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
