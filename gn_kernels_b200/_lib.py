@@ -30,6 +30,8 @@ _SIGNATURES = {
     "gnk_device_status": (c_int, [POINTER(c_int), POINTER(c_uint32), c_int]),
     "gnk_absmax_scratch_bytes": (c_size_t, [c_int64]),
     "gnk_absmax": (c_int, [_P, c_int, c_int64, c_float, _P, _P, _P]),
+    "gnk_absmax_static_max_elems": (c_int64, []),
+    "gnk_absmax_static": (c_int, [_P, c_int, c_int64, c_float, _P, _P]),
     "gnk_quant_rowwise": (c_int, [_P, c_int, c_int64, c_int64, c_int64, c_int, _P, _P, c_int64, c_int64, _P]),
     "gnk_quant_mx": (c_int, [_P, c_int, c_int64, c_int64, c_int64, c_int, c_int, _P, _P, c_int, _P]),
     "gnk_quant_nvfp4": (c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_float, _P, _P, c_int, _P]),

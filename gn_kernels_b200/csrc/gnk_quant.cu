@@ -11,6 +11,7 @@
 //     first correction makes the estimate faithful, the second makes it exact);
 //   * narrow formats are produced by the cvt.rn.satfinite instructions, which round to
 //     nearest even exactly like the reference's casts and threshold chains.
+#include <mutex>
 #include <type_traits>
 
 #include "gnk_common.cuh"
@@ -506,4 +507,71 @@ extern "C" int gnk_dequant_block(const void* q, const uint8_t* sf, int64_t M, in
       static_cast<const uint8_t*>(q), sf, M, K, qkind, block, tensor_scale, out);
   GNK_LAUNCH_OK();
   return GNK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// gnk_absmax_static: the same reduction for callers that cannot provide scratch memory.
+//
+// Some hosts of this library hold no allocator they could call for it: a serving runtime that
+// has handed every byte of device memory to its own arena, or a plugin boundary that passes
+// raw input/output pointers and nothing else.  Calling cudaMalloc from such a place is either
+// impossible (no memory left outside the arena) or unwelcome (it synchronises the device in the
+// middle of a latency-critical loop).  For them the scratch lives in the library image itself:
+// a fixed array in device global memory that every GPU loading the library carries until the
+// process exits.
+// ---------------------------------------------------------------------------------------------
+namespace gnk {
+namespace {
+
+constexpr int64_t kStaticAbsmaxMaxElems = 1ll << 32;  // documented limit of gnk_absmax_static
+// ticket word + one partial maximum per CTA (the kernel never launches more than kAbsmaxMaxCtas CTAs)
+static __device__ __align__(256) unsigned int g_static_absmax_scratch[1 + kAbsmaxMaxCtas];
+
+// Device address of the array above, per device.  The array's name is only a host-side handle;
+// the address a kernel can use has to be asked for with the owning device current.
+std::mutex g_static_mu;
+unsigned int* g_static_ptr[64];
+
+int static_scratch_for_current_device(unsigned int** out) {
+  int dev = 0;
+  GNK_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return GNK_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    GNK_CUDA_OK(cudaGetSymbolAddress(&p, g_static_absmax_scratch));
+    g_static_ptr[dev] = static_cast<unsigned int*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return GNK_OK;
+}
+
+}  // namespace
+}  // namespace gnk
+
+extern "C" int64_t gnk_absmax_static_max_elems(void) { return kStaticAbsmaxMaxElems; }
+
+extern "C" int gnk_absmax_static(const void* x, int dtype, int64_t n, float divisor, float* out,
+                                 gnk_stream_t stream) {
+  if (!x || !out || n <= 0 || !(divisor > 0.f)) return GNK_ERR_BAD_ARG;
+  if (n > kStaticAbsmaxMaxElems) return GNK_ERR_TOO_LARGE;  // beyond what the built-in scratch is specified for
+  if (!aligned16(x)) return GNK_ERR_BAD_ALIGN;
+  unsigned int* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != GNK_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  Only the ticket word has to start at zero;
+  // the partial maxima are overwritten before they are read.
+  GNK_CUDA_OK(cudaMemsetAsync(scratch, 0, sizeof(unsigned int), st));
+  int64_t want = (n / 8 + kAbsmaxThreads - 1) / kAbsmaxThreads;
+  int grid = static_cast<int>(want < 1 ? 1 : (want > kAbsmaxMaxCtas ? kAbsmaxMaxCtas : want));
+  const int cap = num_sms() * 8;
+  if (grid > cap) grid = cap;
+  if (grid > kAbsmaxMaxCtas) grid = kAbsmaxMaxCtas;
+  return dispatch_dtype(dtype, [&](auto* tag) -> int {
+    using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
+    absmax_kernel<T><<<grid, kAbsmaxThreads, 0, st>>>(static_cast<const T*>(x), n, out, divisor, scratch);
+    GNK_LAUNCH_OK();
+    return (int)GNK_OK;
+  });
 }

@@ -68,6 +68,19 @@ size_t gnk_absmax_scratch_bytes(int64_t n);
 int gnk_absmax(const void* x, int dtype, int64_t n, float divisor, float* out, void* scratch,
                gnk_stream_t stream);
 
+/* gnk_absmax without caller-provided scratch.  No counterpart in the reference: it exists for
+ * hosts that cannot allocate on the library's behalf - a runtime whose arena already owns all
+ * device memory, or a binding that passes nothing but input/output pointers - and for which a
+ * cudaMalloc inside the call would be impossible or would stall a serving loop.  The scratch is a
+ * fixed 8 KB array inside the library image (each GPU that loads the library carries it until
+ * exit); the call allocates nothing.  Limit: n <= gnk_absmax_static_max_elems() (2^32), larger n
+ * returns GNK_ERR_TOO_LARGE.  The first call on a device looks up the array's device address;
+ * make that first call before any stream capture begins.  All calls share the one array, so two
+ * calls that overlap on the GPU (different streams, or different host threads) race: serialise them.
+ * Same result as gnk_absmax. */
+int64_t gnk_absmax_static_max_elems(void);
+int gnk_absmax_static(const void* x, int dtype, int64_t n, float divisor, float* out, gnk_stream_t stream);
+
 /* Row-wise absmax quantizer: one fp32 scale per row of `cols` contiguous elements.
  * scale = amax/qmax (127 for INT8, 448 for E4M3); q = x / max(scale, 1e-6); INT8 rounds
  * half-to-even and clips to [-128,127]; E4M3 clips to +-448 then rounds to nearest even.
