@@ -50,6 +50,7 @@ _SIGNATURES = {
     "gnk_gemm_rs_bf16": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), POINTER(c_void_p), _P, c_int64, c_int64, c_int64,
                                  c_int64, c_int, c_int, c_uint32, _P]),
     "gnk_debug_force_tile": (c_int, [c_int]),
+    "gnk_debug_staged": (c_int, [c_int]),
     "gnk_debug_max_clusters": (c_int, [c_int]),
     "gnk_debug_trace": (c_int, [_P]),
 }

@@ -35,10 +35,10 @@ struct ElemInfo {
   static constexpr int kSfBlock = KIND == MmaKind::MXF8F6F4 ? 32 : 16;
 };
 
-template <MmaKind KIND, int BN, int CG, int EPI>
+template <MmaKind KIND, int BN, int CG, int EPI, bool STG = true>
 int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA, const uint8_t* SFB,
            GemmArgs g, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
-  using C = Cfg<KIND, BN, CG, EPI>;
+  using C = Cfg<KIND, BN, CG, EPI, STG>;
   using EI = ElemInfo<KIND>;
   const int64_t k_bytes = K * EI::kNum / EI::kDen;
   const int64_t lda_b = lda * EI::kNum;  // ld counts stored elements (bytes for packed fp4)
@@ -69,7 +69,7 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   g.tiles_m = static_cast<int>((M + 128 * CG - 1) / (128 * CG));
   g.tiles_n = static_cast<int>((N + BN - 1) / BN);
   const int tiles = g.tiles_m * g.tiles_n;
-  auto kern = gemm_kernel<KIND, BN, CG, EPI>;
+  auto kern = gemm_kernel<KIND, BN, CG, EPI, STG>;
   // Persistent grid = the number of clusters that can be resident at once.  For 2-CTA
   // clusters this can be below SMs / 2 (both CTAs must land on one SM pair), and a cluster
   // that does not fit the first wave would run its whole share of tiles after everyone else.
@@ -109,6 +109,7 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
 // Tile choice: the largest tile that still gives every SM work; 2-CTA 256x256 for big problems.
 enum TileSel { T_2x256, T_1x256, T_1x128, T_1x64 };
 int g_force_tile = -1;  // test hook (gnk_debug_force_tile)
+int g_staged = -1;      // test hook (gnk_debug_staged)
 
 TileSel pick_tile(int64_t M, int64_t N, bool block_scaled) {
   if (g_force_tile >= 0) return static_cast<TileSel>(g_force_tile);
@@ -125,7 +126,11 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
                   const GemmArgs& g, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
   constexpr bool kBS = KindInfo<KIND>::kBlockScaled;
   switch (pick_tile(M, N, kBS)) {
-    case T_2x256: return launch<KIND, 256, 2, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+    case T_2x256:
+      // staged (coalesced) epilogue costs pipeline stages; g_staged: -1 = per-kind default, 0 = off, 1 = on
+      if (g_staged == 0 || (g_staged < 0 && kBS))
+        return launch<KIND, 256, 2, EPI, false>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+      return launch<KIND, 256, 2, EPI, true>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x256: return launch<KIND, 256, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x128: return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x64:
@@ -173,6 +178,12 @@ extern "C" int gnk_debug_force_tile(int sel) {
 // Debug: device buffer (2 CTAs x 2 roles x 256 stages x 3 int64 clock stamps) or NULL to stop tracing.
 extern "C" int gnk_debug_trace(void* device_buffer) {
   g_trace = static_cast<long long*>(device_buffer);
+  return GNK_OK;
+}
+
+// Debug: staged epilogue of the 256x256 pair tile: -1 = default per kind, 0 = direct stores, 1 = staged.
+extern "C" int gnk_debug_staged(int mode) {
+  g_staged = mode;
   return GNK_OK;
 }
 

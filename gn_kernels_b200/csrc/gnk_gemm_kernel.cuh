@@ -46,12 +46,12 @@ struct GemmArgs {
   } rs;
 };
 
-template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16>
+template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16, bool STG = true>
 struct Cfg {
   using KI = KindInfo<KIND>;
   // bf16 outputs of the 256-wide pair tile leave through a per-warp shared-memory staging area
   // (32 rows x BN) so that every global store instruction writes one whole 512-byte row segment
-  static constexpr bool kStaged = BN == 256 && CG == 2 && EPI != EPI_I32;
+  static constexpr bool kStaged = STG && BN == 256 && CG == 2 && EPI != EPI_I32;
   static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : 0;
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = (BN / CG) * 128;
@@ -244,12 +244,12 @@ __device__ __forceinline__ void flush_smem_rows(uint32_t stg, int lane, __nv_bfl
   }
 }
 
-template <MmaKind KIND, int BN, int CG, int EPI>
+template <MmaKind KIND, int BN, int CG, int EPI, bool STG = true>
 __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                 const GemmArgs g) {
-  using C = Cfg<KIND, BN, CG, EPI>;
+  using C = Cfg<KIND, BN, CG, EPI, STG>;
   constexpr bool kBS = C::KI::kBlockScaled;
   constexpr int S = C::kStages;
   constexpr int kInner = KIND == MmaKind::F16 ? 64 : 128;  // tensor-map elements per 128-byte K stage

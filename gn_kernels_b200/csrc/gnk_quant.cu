@@ -160,55 +160,90 @@ __global__ void __launch_bounds__(256) quant_rowwise_kernel(const T* __restrict_
   const int lane = threadIdx.x & 31;
   const int sub = lane % LPR;
   const int64_t rows_per_cta = (256 / LPR);
-  const int64_t row = blockIdx.x * rows_per_cta + threadIdx.x / LPR;
-  const bool live = row < rows;
-  const T* xr = x + (live ? row : 0) * ldx;
+  const float qmax = QKIND == GNK_Q_INT8 ? 127.f : 448.f;
+  const bool one_shot = cols <= LPR * 8;  // the row is one 8-element group per lane: read it once
+  // persistent CTAs walk over groups of rows_per_cta rows
+  for (int64_t rg = blockIdx.x; rg * rows_per_cta < rows; rg += gridDim.x) {
+    const int64_t row = rg * rows_per_cta + threadIdx.x / LPR;
+    const bool live = row < rows;
+    const T* xr = x + (live ? row : 0) * ldx;
+    float first[8];
+    float m = 0.f;
+    if (live) {
+      if (one_shot) {
+        if (sub * 8 < cols) {
+          load8<T>(xr + sub * 8, first);
+          m = amax8(first);
+        }
+      } else {
+        int64_t c = sub * 8;
+        for (; c + 3 * LPR * 8 < cols; c += 4 * LPR * 8) {  // four independent loads in flight
+          float v[4][8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) load8<T>(xr + c + j * LPR * 8, v[j]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) m = fmaxf(m, amax8(v[j]));
+        }
+        for (; c < cols; c += LPR * 8) {
+          float v[8];
+          load8<T>(xr + c, v);
+          m = fmaxf(m, amax8(v));
+        }
+      }
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (!live) continue;
 
-  float m = 0.f;
-  if (live)
-    for (int64_t c = sub * 8; c < cols; c += LPR * 8) {
+    const float s = __fdiv_rn(m, qmax);
+    const float d = fmaxf(s, 1e-6f);
+    const float r = __frcp_rn(d);
+    const bool safe = m >= 1e-30f;  // quotients are <= qmax * (1 + eps) then; tiny rows take the slow path
+    if (sub == 0) {
+      int64_t idx = row;
+      if (perm_h > 0) {
+        const int64_t h = row % perm_h, bl = row / perm_h, l = bl % perm_l, b = bl / perm_l;
+        idx = (b * perm_h + h) * perm_l + l;
+      }
+      scale[idx] = s;
+    }
+    uint8_t* qr = q + row * cols;
+    auto encode = [&](float (&v)[8], int64_t c) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = divide_exact(v[i], d, r, safe);
+      uint2 out;
+      if constexpr (QKIND == GNK_Q_INT8) {
+        uint32_t b[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float t = fminf(fmaxf(rintf(v[i]), -128.f), 127.f);
+          b[i] = static_cast<uint32_t>(static_cast<int>(t)) & 0xFFu;
+        }
+        out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+        out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+      } else {
+        out.x = cvt_e4m3x2(v[0], v[1]) | (cvt_e4m3x2(v[2], v[3]) << 16);
+        out.y = cvt_e4m3x2(v[4], v[5]) | (cvt_e4m3x2(v[6], v[7]) << 16);
+      }
+      *reinterpret_cast<uint2*>(qr + c) = out;
+    };
+    if (one_shot) {
+      if (sub * 8 < cols) encode(first, sub * 8);
+      continue;
+    }
+    int64_t c = sub * 8;
+    for (; c + 3 * LPR * 8 < cols; c += 4 * LPR * 8) {  // the row is in L1/L2 now
+      float v[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) load8<T>(xr + c + j * LPR * 8, v[j]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) encode(v[j], c + j * LPR * 8);
+    }
+    for (; c < cols; c += LPR * 8) {
       float v[8];
       load8<T>(xr + c, v);
-      m = fmaxf(m, amax8(v));
+      encode(v, c);
     }
-#pragma unroll
-  for (int o = LPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (!live) return;
-
-  const float qmax = QKIND == GNK_Q_INT8 ? 127.f : 448.f;
-  const float s = __fdiv_rn(m, qmax);
-  const float d = fmaxf(s, 1e-6f);
-  const float r = __frcp_rn(d);
-  const bool safe = m >= 1e-30f;  // quotients are <= qmax * (1 + eps) then; tiny rows take the slow path
-  if (sub == 0) {
-    int64_t idx = row;
-    if (perm_h > 0) {
-      const int64_t h = row % perm_h, bl = row / perm_h, l = bl % perm_l, b = bl / perm_l;
-      idx = (b * perm_h + h) * perm_l + l;
-    }
-    scale[idx] = s;
-  }
-  uint8_t* qr = q + row * cols;
-  for (int64_t c = sub * 8; c < cols; c += LPR * 8) {
-    float v[8];
-    load8<T>(xr + c, v);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = divide_exact(v[i], d, r, safe);
-    uint2 out;
-    if constexpr (QKIND == GNK_Q_INT8) {
-      uint32_t b[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float t = fminf(fmaxf(rintf(v[i]), -128.f), 127.f);
-        b[i] = static_cast<uint32_t>(static_cast<int>(t)) & 0xFFu;
-      }
-      out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-      out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
-    } else {
-      out.x = cvt_e4m3x2(v[0], v[1]) | (cvt_e4m3x2(v[2], v[3]) << 16);
-      out.y = cvt_e4m3x2(v[4], v[5]) | (cvt_e4m3x2(v[6], v[7]) << 16);
-    }
-    *reinterpret_cast<uint2*>(qr + c) = out;
   }
 }
 
@@ -220,9 +255,10 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const T* __restrict__ x, 
                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                                        int swizzled, int64_t rows_out, int64_t ks_out) {
   const int64_t ks = K >> 5;
-  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (idx >= rows_out * ks_out) return;
-  const int64_t row = idx / ks_out, kb = idx % ks_out;
+  const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;  // the launcher keeps rows_out * ks_out below 2^31
+  if (idx >= static_cast<unsigned>(rows_out * ks_out)) return;
+  const unsigned urow = idx / static_cast<unsigned>(ks_out);
+  const int64_t row = urow, kb = idx - urow * static_cast<unsigned>(ks_out);
   if (row >= M || kb >= ks) {  // padding of the swizzled layout
     sf[sf_offset(row, kb, ks_out, true, ks)] = 0;
     return;
@@ -288,9 +324,10 @@ __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const T* __restrict__ 
                                                           uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                                           int swizzled, int64_t rows_out, int64_t ks_out) {
   const int64_t ks = K >> 4;
-  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (idx >= rows_out * ks_out) return;
-  const int64_t row = idx / ks_out, kb = idx % ks_out;
+  const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;  // the launcher keeps rows_out * ks_out below 2^31
+  if (idx >= static_cast<unsigned>(rows_out * ks_out)) return;
+  const unsigned urow = idx / static_cast<unsigned>(ks_out);
+  const int64_t row = urow, kb = idx - urow * static_cast<unsigned>(ks_out);
   if (row >= M || kb >= ks) {
     sf[sf_offset(row, kb, ks_out, true, ks)] = 0;
     return;
@@ -398,7 +435,9 @@ static int launch_rowwise(const T* x, int64_t rows, int64_t cols, int64_t ldx, u
   int lpr = 32;
   while (lpr > 1 && (lpr / 2) * 8 >= cols) lpr /= 2;
   const int64_t rows_per_cta = 256 / lpr;
-  const unsigned grid = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta);
+  const int64_t groups = (rows + rows_per_cta - 1) / rows_per_cta;
+  const int64_t cap = static_cast<int64_t>(num_sms()) * 8;  // persistent: 8 CTAs of 256 threads per SM
+  const unsigned grid = static_cast<unsigned>(groups < cap ? groups : cap);
 #define GNK_RW(L)                                                                                          \
   case L:                                                                                                  \
     quant_rowwise_kernel<T, QKIND, L><<<grid, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); \
@@ -441,7 +480,7 @@ extern "C" int gnk_quant_mx(const void* x, int dtype, int64_t M, int64_t K, int6
   const int64_t rows_out = sf_swizzled ? (M + 127) / 128 * 128 : M;
   const int64_t ks_out = sf_swizzled ? (ks + 3) / 4 * 4 : ks;
   const int64_t nblk = (rows_out * ks_out + 255) / 256;
-  if (nblk > 0x7FFFFFFF) return GNK_ERR_TOO_LARGE;
+  if (nblk > 0x7FFFFFFF / 256) return GNK_ERR_TOO_LARGE;
   const unsigned grid = static_cast<unsigned>(nblk);
   return dispatch_dtype(dtype, [&](auto* tag) -> int {
     using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
@@ -474,7 +513,7 @@ extern "C" int gnk_quant_nvfp4(const void* x, int dtype, int64_t M, int64_t K, i
   const int64_t rows_out = sf_swizzled ? (M + 127) / 128 * 128 : M;
   const int64_t ks_out = sf_swizzled ? (ks + 3) / 4 * 4 : ks;
   const int64_t nblk = (rows_out * ks_out + 255) / 256;
-  if (nblk > 0x7FFFFFFF) return GNK_ERR_TOO_LARGE;
+  if (nblk > 0x7FFFFFFF / 256) return GNK_ERR_TOO_LARGE;
   const unsigned grid = static_cast<unsigned>(nblk);
   return dispatch_dtype(dtype, [&](auto* tag) -> int {
     using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
