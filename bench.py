@@ -1,28 +1,33 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized-matmul hot path on B200.
+"""Benchmark of the quantized-matmul / quantizer / attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 Default workload: MXFP8 GEMM, M = N = K = 8192 (E4M3 values, one E8M0 scale per 32 K
 elements, fp32 accumulate, bf16 output), synthetic N(0,1) data quantised on the GPU
-before the timed region.  One "step" = one GEMM over resident operands.  The JSON line
-carries: `value` (device-timed TFLOP/s, whole job), `e2e` (same GEMM through the public
-Python API from pinned HOST buffers, copies inside the timed region), `roofline` for the
-GEMM kernel, `cpu_baseline` (the oracle's dequantise-then-matmul on the host cores, on a
-bounded row sample), and sampled SM clocks.
+before the timed region.  One "step" = one pass of the workload's kernel over resident
+operands.  The JSON line carries: `value` (device-timed, whole job), `e2e` (the same call
+through the public Python API from pinned HOST buffers, copies inside the timed region),
+`roofline` for the kernel, `cpu_baseline` (the oracle on the host cores, bounded sample),
+and the SM clocks sampled while the GPU was in the loaded state the timed steps ran in.
 
-With --gpus N > 1 (under torchrun) every rank runs the same GEMM on its own GPU: the GEMM
-does not shard ("replicas only"), so scaling is weak and `value` is the sum over ranks.
+Other workloads (--workload): NVFP4 / INT8 / BF16 GEMMs, skinny MXFP8 decode shapes, the
+NVFP4 quantizer (GB/s) and the FP8-QK causal GQA attention of the reference's benchmark
+configuration.  With --gpus N > 1 (under torchrun) every rank runs the same workload on
+its own GPU: these ops do not shard ("replicas only"), scaling is weak and `value` is the
+sum over ranks.  The K-sharded GEMM + reduce-scatter has its own driver
+(tests/gemm_rs_worker.py --bench) because it needs symmetric memory across ranks.
 
 --impl reference times the CPU restatement of the upstream torch reference path
-(oracle/) on the host cores with every thread torch can use, on the same workload and
-metric, each step a bounded sample of the rows.
+(oracle/) on the host cores with every thread torch can use, same workload and metric,
+each step a bounded sample.
 """
 
 from __future__ import annotations
 
 import argparse
 import ctypes
+import datetime
 import json
 import os
 import subprocess
@@ -36,22 +41,29 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-SEED = 2025 * 2024 + 2027  # upstream benchmark_mm.py:36
-
-WORKLOADS = {
-    # name: (metric, M, N, K)
-    "mxfp8_gemm_8192": ("MXFP8 GEMM TFLOPS at M=N=K=8192", 8192, 8192, 8192),
-    "nvfp4_gemm_8192": ("NVFP4 GEMM TFLOPS at M=N=K=8192", 8192, 8192, 8192),
-    "int8_gemm_8192": ("row-scaled INT8 GEMM TOPS at M=N=K=8192", 8192, 8192, 8192),
-    "int8_gemm_1024": ("row-scaled INT8 GEMM TOPS at M=N=K=1024", 1024, 1024, 1024),
-    "bf16_gemm_8192": ("BF16 GEMM TFLOPS at M=N=K=8192", 8192, 8192, 8192),
-}
+SEED_MM = 2025 * 2024 + 2027  # upstream benchmark_mm.py:36
+SEED_ATTN = 2025 * 2026  # upstream benchmark_attn.py:66
+L2_BYTES = 126 * 2**20
+SPEC_BF16_TFLOPS = 2250.0
 # dense tensor-core rate of each kind relative to bf16 (B200: fp8/int8 2x, fp4 4x)
 RATE_VS_BF16 = {"mxfp8": 2.0, "nvfp4": 4.0, "int8": 2.0, "bf16": 1.0}
-SPEC_BF16_TFLOPS = 2250.0
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the 2-CTA GEMM kernel
-# from the committed ncu captures (profiles/gemm_*.md); None where no capture exists yet.
-NCU_TRAFFIC_BYTES = {"mxfp8_gemm_8192": None, "bf16_gemm_8192": 1.098e9 + 0.160e9}
+
+# name -> (family, metric, shape)
+WORKLOADS = {
+    "mxfp8_gemm_8192": ("gemm", "MXFP8 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
+    "nvfp4_gemm_8192": ("gemm", "NVFP4 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
+    "int8_gemm_8192": ("gemm", "row-scaled INT8 GEMM TOPS at M=N=K=8192", (8192, 8192, 8192)),
+    "int8_gemm_1024": ("gemm", "row-scaled INT8 GEMM TOPS at M=N=K=1024", (1024, 1024, 1024)),
+    "bf16_gemm_8192": ("gemm", "BF16 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
+    "mxfp8_gemm_m16": ("gemm", "MXFP8 GEMM TFLOPS at M=16, N=K=8192", (16, 8192, 8192)),
+    "mxfp8_gemm_m64": ("gemm", "MXFP8 GEMM TFLOPS at M=64, N=K=8192", (64, 8192, 8192)),
+    "mxfp8_gemm_m128": ("gemm", "MXFP8 GEMM TFLOPS at M=128, N=K=8192", (128, 8192, 8192)),
+    "nvfp4_quant_8192": ("quant", "NVFP4 quantizer GB/s at 8192x8192 bf16", (8192, 8192)),
+    "attn_fp8_causal": ("attn", "FP8-QK causal GQA attention TFLOPS (B=4, Hq=32, Hkv=8, L=4096, D=128)", (4, 4096, 32, 8, 128)),
+}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures
+# under profiles/; None where no capture of that workload exists.
+NCU_TRAFFIC_BYTES = {"mxfp8_gemm_8192": 364.0e6 + 116.8e6}
 
 
 def load_peaks():
@@ -59,19 +71,17 @@ def load_peaks():
     if os.path.exists(path):
         with open(path) as fh:
             p = json.load(fh)
-        return {"hbm_gbs": p["hbm_gbs"], "bf16": p["bf16_tflops"], "bf16_sustained": p.get("bf16_tflops_sustained"), "src": "measured"}
+        return {"hbm_gbs": p["hbm_gbs"], "bf16": p["bf16_tflops"], "bf16_sustained": p.get("bf16_tflops_sustained") or p["bf16_tflops"], "src": "measured"}
     return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "src": "fallback"}
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the GPU is loaded."""
 
     Q = "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.path = None
+        self.index, self.proc, self.path = index, None, None
 
     def start(self):
         try:
@@ -80,16 +90,13 @@ class ClockSampler:
             self.fh = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=self.fh,
-                stderr=subprocess.DEVNULL,
+                stdout=self.fh, stderr=subprocess.DEVNULL,
             )
         except Exception:
             self.proc = None
 
-    def stop(self, t_begin: float | None = None, t_end: float | None = None) -> dict:
+    def stop(self, t_begin: float, t_end: float) -> dict:
         """Median SM clock over the samples whose timestamp lies in [t_begin, t_end] (wall clock)."""
-        import datetime
-
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -110,7 +117,7 @@ class ClockSampler:
                     clk, cmax = float(f[1]), float(f[2])
                 except ValueError:
                     continue
-                if t_begin is not None and not (t_begin <= ts <= t_end):
+                if not (t_begin <= ts <= t_end):
                     continue
                 clocks.append(clk)
                 mx = cmax
@@ -123,137 +130,196 @@ class ClockSampler:
         return out
 
 
+def _pin(t: torch.Tensor) -> torch.Tensor:
+    p = torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory()
+    if t.element_size() == 1:
+        p.view(torch.uint8).copy_(t.view(torch.uint8))
+    else:
+        p.copy_(t)
+    return p
+
+
+def _nbytes(ts) -> int:
+    return int(sum(t.numel() * t.element_size() for t in ts))
+
+
 # ------------------------------------------------------------------------------------------
-# workload construction (GPU arm)
+# GPU arm
 # ------------------------------------------------------------------------------------------
-def build_gpu_workload(name: str, dev: torch.device):
-    """Returns (step_fn(), host_step_fn or None, info) with operands resident on `dev`."""
+def build_gpu_workload(name: str, dev: torch.device) -> dict:
+    """Operands resident on `dev`; returns step() (C ABI, preallocated outputs), host_step()
+    (public API from pinned host buffers, result read back) and the accounting."""
     import gn_kernels_b200 as gk
     from gn_kernels_b200 import _lib, ops
 
     L = _lib.lib()
-    metric, M, N, K = WORKLOADS[name]
-    g = torch.Generator(device="cpu").manual_seed(SEED)
-    A = torch.randn(M, K, generator=g, dtype=torch.float32).to(dev)
-    Bt = torch.randn(N, K, generator=g, dtype=torch.float32).to(dev)
+    family, metric, shape = WORKLOADS[name]
     P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
     stream = lambda: ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)  # noqa: E731
-    C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     kind = name.split("_")[0]
+    w = {"family": family, "metric": metric, "kind": kind, "config": {}}
 
-    if kind == "mxfp8":
-        Aq, sfa = gk.quantize_mx(A.bfloat16(), torch.float8_e4m3fn, swizzled_scales=True)
-        Bq, sfb = gk.quantize_mx(Bt.bfloat16(), torch.float8_e4m3fn, swizzled_scales=True)
-        step = lambda: L.gnk_mm_mxfp8(P(Aq), K, P(Bq), K, P(sfa), P(sfb), P(C), N, M, N, K, stream())  # noqa: E731
-        host_in = [Aq, Bq, sfa, sfb]
-        api = lambda a, b, sa, sb: gk.cutedsl.sm100.sm100_mm_mxfp8.mm(a, b, sa, sb)  # noqa: E731
-    elif kind == "nvfp4":
-        tsa, tsb = ops.absmax(A, 2688.0), ops.absmax(Bt, 2688.0)
-        Aq, sfa = gk.quantize_nvfp4_triton(A.bfloat16(), tsa)
-        Bq, sfb = gk.quantize_nvfp4_triton(Bt.bfloat16(), tsb)
-        alpha = float(tsa) * float(tsb)
-        step = lambda: L.gnk_mm_nvfp4(P(Aq), K // 2, P(Bq), K // 2, P(sfa), P(sfb), alpha, P(C), N, M, N, K, stream())  # noqa: E731
-        host_in = [Aq, Bq, sfa, sfb]
-        api = lambda a, b, sa, sb: gk.cutedsl.sm100.sm100_mm_nvfp4.mm(a, b, sa, sb, alpha)  # noqa: E731
-    elif kind == "int8":
-        Aq, sA = gk.quantize_rowwise(A, torch.int8)
-        Bq, sB = gk.quantize_rowwise(Bt, torch.int8)
-        sA, sB = sA.view(M, 1), sB.view(1, N)
-        step = lambda: L.gnk_mm_i8(P(Aq), K, P(Bq), K, P(C), N, M, N, K, P(sA), P(sB), None, 0, stream())  # noqa: E731
-        host_in = [Aq, Bq, sA, sB]
-        api = lambda a, b, sa, sb: gk.triton_mm(a, b.T, scale_A=sa, scale_B=sb)  # noqa: E731
-    elif kind == "bf16":
-        Ab, Bb = A.bfloat16(), Bt.bfloat16()
-        step = lambda: L.gnk_mm_bf16(P(Ab), K, P(Bb), K, P(C), N, M, N, K, stream())  # noqa: E731
-        host_in = [Ab, Bb]
-        api = lambda a, b: gk.cutedsl.sm100.sm100_mm_bf16.mm(a, b.T)  # noqa: E731
+    if family == "gemm":
+        M, N, K = shape
+        g = torch.Generator(device="cpu").manual_seed(SEED_MM)
+        A = torch.randn(M, K, generator=g, dtype=torch.float32).to(dev)
+        Bt = torch.randn(N, K, generator=g, dtype=torch.float32).to(dev)
+        C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        if kind == "mxfp8":
+            Aq, sfa = gk.quantize_mx(A.bfloat16(), torch.float8_e4m3fn, swizzled_scales=True)
+            Bq, sfb = gk.quantize_mx(Bt.bfloat16(), torch.float8_e4m3fn, swizzled_scales=True)
+            step = lambda: L.gnk_mm_mxfp8(P(Aq), K, P(Bq), K, P(sfa), P(sfb), P(C), N, M, N, K, stream())  # noqa: E731
+            ins = [Aq, Bq, sfa, sfb]
+            api = lambda a, b, sa, sb: gk.cutedsl.sm100.sm100_mm_mxfp8.mm(a, b, sa, sb)  # noqa: E731
+            algo_bytes = N * K + N * K // 32 + M * K + M * K // 32 + 2 * M * N
+        elif kind == "nvfp4":
+            tsa, tsb = ops.absmax(A, 2688.0), ops.absmax(Bt, 2688.0)
+            Aq, sfa = gk.quantize_nvfp4_triton(A.bfloat16(), tsa)
+            Bq, sfb = gk.quantize_nvfp4_triton(Bt.bfloat16(), tsb)
+            alpha = float(tsa) * float(tsb)
+            step = lambda: L.gnk_mm_nvfp4(P(Aq), K // 2, P(Bq), K // 2, P(sfa), P(sfb), alpha, P(C), N, M, N, K, stream())  # noqa: E731
+            ins = [Aq, Bq, sfa, sfb]
+            api = lambda a, b, sa, sb: gk.cutedsl.sm100.sm100_mm_nvfp4.mm(a, b, sa, sb, alpha)  # noqa: E731
+            algo_bytes = (M + N) * (K // 2 + K // 16) + 2 * M * N
+        elif kind == "int8":
+            Aq, sA = gk.quantize_rowwise(A, torch.int8)
+            Bq, sB = gk.quantize_rowwise(Bt, torch.int8)
+            sA, sB = sA.view(M, 1), sB.view(1, N)
+            step = lambda: L.gnk_mm_i8(P(Aq), K, P(Bq), K, P(C), N, M, N, K, P(sA), P(sB), None, 0, stream())  # noqa: E731
+            ins = [Aq, Bq, sA, sB]
+            api = lambda a, b, sa, sb: gk.triton_mm(a, b.T, scale_A=sa, scale_B=sb)  # noqa: E731
+            algo_bytes = (M + N) * K + 2 * M * N
+        else:
+            Ab, Bb = A.bfloat16(), Bt.bfloat16()
+            step = lambda: L.gnk_mm_bf16(P(Ab), K, P(Bb), K, P(C), N, M, N, K, stream())  # noqa: E731
+            ins = [Ab, Bb]
+            api = lambda a, b: gk.cutedsl.sm100.sm100_mm_bf16.mm(a, b.T)  # noqa: E731
+            algo_bytes = 2 * (M + N) * K + 2 * M * N
+        w.update(work=2.0 * M * N * K, unit="TOP/s" if kind == "int8" else "TFLOP/s", scale=1e12, ins=ins, outs=[C], api=api, step=step,
+                 algo_bytes=algo_bytes, bound="hbm" if M <= 128 else "tensor", config={"M": M, "N": N, "K": K})
+    elif family == "quant":
+        M, K = shape
+        g = torch.Generator(device="cpu").manual_seed(SEED_MM)
+        x = torch.randn(M, K, generator=g, dtype=torch.float32).bfloat16().to(dev)
+        ts = ops.absmax(x, 2688.0)
+        q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+        sf = torch.empty(M, K // 16, dtype=torch.uint8, device=dev)
+        step = lambda: L.gnk_quant_nvfp4(P(x), 0, M, K, K, P(ts), 1e-12, P(q), P(sf), 1, stream())  # noqa: E731
+        api = lambda xx: gk.quantize_nvfp4_triton(xx, ts)[0]  # noqa: E731
+        nbytes = 2 * M * K + M * K // 2 + M * K // 16
+        w.update(work=float(nbytes), unit="GB/s", scale=1e9, ins=[x], outs=[q, sf], api=api, step=step, algo_bytes=nbytes, bound="hbm",
+                 config={"M": M, "K": K, "tensor_scale": "precomputed amax/(6*448), not in the timed step"})
     else:
-        raise ValueError(name)
+        B, Lq, Hq, Hkv, D = shape
+        g = torch.Generator(device="cpu").manual_seed(SEED_ATTN)
+        qf = torch.randn(B, Lq, Hq, D, generator=g).bfloat16().to(dev)
+        kf = torch.randn(B, Lq, Hkv, D, generator=g).bfloat16().to(dev)
+        v = torch.randn(B, Lq, Hkv, D, generator=g).bfloat16().to(dev)
+        qq, sq = gk.quantize_rowwise(qf, torch.float8_e4m3fn, transpose_scales=True)
+        kq, sk = gk.quantize_rowwise(kf, torch.float8_e4m3fn, transpose_scales=True)
+        o = torch.empty(B, Lq, Hq, D, dtype=torch.bfloat16, device=dev)
+        I3 = ctypes.c_int64 * 3
+        st = [I3(*t.stride()[:3]) for t in (qq, kq, v, o)]
+        step = lambda: L.gnk_attn_fwd(P(qq), P(kq), P(v), P(o), P(sq), P(sk), 1, B, Lq, Lq, Hq, Hkv, D, st[0], st[1], st[2], st[3], 1, stream())  # noqa: E731
+        api = lambda a, b, c, d, e: gk.triton_attn(a, b, c, d, e, causal=True)  # noqa: E731
+        w.update(work=4.0 * B * Hq * Lq * Lq * D / 2, unit="TFLOP/s", scale=1e12, ins=[qq, kq, v, sq, sk], outs=[o], api=api, step=step,
+                 algo_bytes=_nbytes([qq, kq, v, sq, sk, o]), bound="tensor",
+                 config={"B": B, "L": Lq, "Hq": Hq, "Hkv": Hkv, "D": D, "causal": True, "flops": "causal half of 4*B*Hq*L*L*D"})
 
-    pinned = [torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for t in host_in]
-    for p, t in zip(pinned, host_in):
-        p.view(torch.uint8).copy_(t.view(torch.uint8)) if t.element_size() == 1 else p.copy_(t)
-    out_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    pinned = [_pin(t) for t in w["ins"]]
+    out0 = w["outs"][0]
+    out_host = torch.empty(out0.shape, dtype=out0.dtype).pin_memory()
 
     def host_step():
         dev_in = [p.to(dev, non_blocking=True) for p in pinned]
-        out = api(*dev_in)
-        out_host.copy_(out, non_blocking=True)
+        out = w["api"](*dev_in)
+        out_host.copy_(out.view(out_host.dtype) if out.dtype != out_host.dtype else out, non_blocking=True)
 
-    info = {
-        "metric": metric, "M": M, "N": N, "K": K, "kind": kind,
-        "flops": 2.0 * M * N * K,
-        "h2d": int(sum(p.numel() * p.element_size() for p in pinned)),
-        "d2h": int(out_host.numel() * out_host.element_size()),
-        "resident_bytes": int(sum(t.numel() * t.element_size() for t in host_in) + C.numel() * 2),
-        "check": (host_in, C),
-    }
-    return step, host_step, info
+    w.update(host_step=host_step, h2d=_nbytes(pinned), d2h=_nbytes([out_host]), resident_bytes=_nbytes(w["ins"]) + _nbytes(w["outs"]))
+    return w
 
 
 # ------------------------------------------------------------------------------------------
-# CPU arm: the oracle's dequantise-then-matmul on a bounded row sample
+# CPU arm: the oracle on a bounded sample of the same workload
 # ------------------------------------------------------------------------------------------
 def build_cpu_workload(name: str, rows: int):
+    from oracle import attn as oattn
     from oracle import mm as omm
     from oracle import quant as oq
 
-    metric, M, N, K = WORKLOADS[name]
+    family, metric, shape = WORKLOADS[name]
     kind = name.split("_")[0]
-    rows = min(rows, M)
-    g = torch.Generator(device="cpu").manual_seed(SEED)
-    A = torch.randn(M, K, generator=g, dtype=torch.float32)[:rows]
-    Bt = torch.randn(N, K, generator=g, dtype=torch.float32)
-    if kind == "mxfp8":
-        Aq, sfa = oq.quantize_mx(A.bfloat16().float().numpy(), "e4m3")
-        Bq, sfb = oq.quantize_mx(Bt.bfloat16().float().numpy(), "e4m3")
-        step = lambda: omm.mm_mxfp8(Aq, Bq, sfa, sfb)  # noqa: E731
-    elif kind == "nvfp4":
-        Aq, sfa, tsa = oq.quantize_nvfp4(A.bfloat16().float().numpy())
-        Bq, sfb, tsb = oq.quantize_nvfp4(Bt.bfloat16().float().numpy())
-        step = lambda: omm.mm_nvfp4(Aq, Bq, sfa, sfb, float(tsa) * float(tsb))  # noqa: E731
-    elif kind == "int8":
-        Aq, sA = oq.quantize_rowwise(A.numpy(), "int8")
-        Bq, sB = oq.quantize_rowwise(Bt.numpy(), "int8")
-        step = lambda: omm.mm_i8_row_scaled(Aq, Bq, sA, sB)  # noqa: E731
-    else:
-        Ab, Bb = A.bfloat16(), Bt.bfloat16()
-        step = lambda: omm.mm_bf16(Ab, Bb)  # noqa: E731
-    return step, {"metric": metric, "flops": 2.0 * rows * N * K, "rows": rows, "M": M, "N": N, "K": K}
+    if family == "gemm":
+        M, N, K = shape
+        rows = min(rows, M)
+        g = torch.Generator(device="cpu").manual_seed(SEED_MM)
+        A = torch.randn(M, K, generator=g, dtype=torch.float32)[:rows]
+        Bt = torch.randn(N, K, generator=g, dtype=torch.float32)
+        if kind == "mxfp8":
+            Aq, sfa = oq.quantize_mx(A.bfloat16().float().numpy(), "e4m3")
+            Bq, sfb = oq.quantize_mx(Bt.bfloat16().float().numpy(), "e4m3")
+            step = lambda: omm.mm_mxfp8(Aq, Bq, sfa, sfb)  # noqa: E731
+        elif kind == "nvfp4":
+            Aq, sfa, tsa = oq.quantize_nvfp4(A.bfloat16().float().numpy())
+            Bq, sfb, tsb = oq.quantize_nvfp4(Bt.bfloat16().float().numpy())
+            step = lambda: omm.mm_nvfp4(Aq, Bq, sfa, sfb, float(tsa) * float(tsb))  # noqa: E731
+        elif kind == "int8":
+            Aq, sA = oq.quantize_rowwise(A.numpy(), "int8")
+            Bq, sB = oq.quantize_rowwise(Bt.numpy(), "int8")
+            step = lambda: omm.mm_i8_row_scaled(Aq, Bq, sA, sB)  # noqa: E731
+        else:
+            Ab, Bb = A.bfloat16(), Bt.bfloat16()
+            step = lambda: omm.mm_bf16(Ab, Bb)  # noqa: E731
+        sample = f"{rows} of {M} rows x all {N} columns, K={K} (dequantise + fp32 matmul + bf16 cast per step)"
+        return step, 2.0 * rows * N * K, sample
+    if family == "quant":
+        M, K = shape
+        rows = min(rows, M)
+        g = torch.Generator(device="cpu").manual_seed(SEED_MM)
+        x = torch.randn(M, K, generator=g, dtype=torch.float32)[:rows].bfloat16().float().numpy()
+        ts = np.float32(np.abs(x).max() / 2688.0)
+        step = lambda: oq.quantize_nvfp4(x, ts)  # noqa: E731
+        return step, float(2 * rows * K + rows * K // 2 + rows * K // 16), f"{rows} of {M} rows (numpy restatement of quantize_nvfp4)"
+    B, L, Hq, Hkv, D = shape
+    g = torch.Generator(device="cpu").manual_seed(SEED_ATTN)
+    heads = 2
+    q = torch.randn(1, L, heads, D, generator=g).bfloat16()
+    k = torch.randn(1, L, 1, D, generator=g).bfloat16()
+    v = torch.randn(1, L, 1, D, generator=g).bfloat16()
+    qq, sq = oq.quantize_rowwise(q.float().numpy(), "e4m3")
+    kq, sk = oq.quantize_rowwise(k.float().numpy(), "e4m3")
+    sq_t = torch.from_numpy(sq).permute(0, 2, 1).contiguous()
+    sk_t = torch.from_numpy(sk).permute(0, 2, 1).contiguous()
+    step = lambda: oattn.attention_qk_quantized(qq, kq, v, sq_t, sk_t, kind="e4m3", causal=True)  # noqa: E731
+    return step, 4.0 * heads * L * L * D / 2, f"1 of {B} batches x {heads} of {Hq} query heads (dequantise + fp32 softmax attention)"
 
 
-def time_cpu(step, steps: int, warmup: int):
+def time_cpu(step, steps: int, warmup: int) -> float:
     for _ in range(warmup):
         step()
-    ts = []
+    t0 = time.perf_counter()
     for _ in range(steps):
-        t0 = time.perf_counter()
         step()
-        ts.append(time.perf_counter() - t0)
-    return float(np.sum(ts)), float(np.median(ts))
-
-
-def unit_for(kind: str) -> str:
-    return "TOP/s" if kind == "int8" else "TFLOP/s"
+    return time.perf_counter() - t0
 
 
 # ------------------------------------------------------------------------------------------
 def run_reference(args, rank: int):
     if rank != 0:
         return
-    step, info = build_cpu_workload(args.workload, args.cpu_rows)
-    total, med = time_cpu(step, args.steps, max(1, min(args.warmup, 1)))
+    family, metric, shape = WORKLOADS[args.workload]
     kind = args.workload.split("_")[0]
-    val = info["flops"] * args.steps / total / 1e12
+    step, work, sample = build_cpu_workload(args.workload, args.cpu_rows)
+    total = time_cpu(step, args.steps, max(1, min(args.warmup, 1)))
+    unit, scale = ("GB/s", 1e9) if family == "quant" else (("TOP/s" if kind == "int8" else "TFLOP/s"), 1e12)
+    val = work * args.steps / total / scale
     cores = torch.get_num_threads()
-    sample = f"{info['rows']} of {info['M']} rows x all {info['N']} columns, K={info['K']} (dequantise + fp32 matmul + bf16 cast per step)"
     line = {
-        "impl": "reference", "metric": info["metric"], "value": val, "unit": unit_for(kind), "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": kind, "data": "synthetic",
-        "config": {"workload": args.workload, "M": info["M"], "N": info["N"], "K": info["K"], "sample": sample},
-        "cpu_baseline": {"value": val, "unit": unit_for(kind), "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": unit_for(kind), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
+        "data": "synthetic", "config": {"workload": args.workload, "shape": list(shape), "sample": sample},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "host_cpus": os.cpu_count(),
     }
     print(json.dumps(line), flush=True)
@@ -268,23 +334,28 @@ def run_gpu(args, rank: int, local_rank: int, world: int):
         dist.init_process_group("nccl", device_id=dev)
     from gn_kernels_b200 import _lib
 
-    step, host_step, info = build_gpu_workload(args.workload, dev)
-    kind = info["kind"]
+    w = build_gpu_workload(args.workload, dev)
+    step = w["step"]
     peaks = load_peaks()
+    flush_buf = None
+    if w["resident_bytes"] < 1.5 * L2_BYTES:  # operands could stay in L2 between steps: flush it
+        flush_buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         rc = step()
         if rc != 0:
             raise RuntimeError(f"kernel launch failed: status {rc}")
     _lib.raise_on_device_error()
 
-    # ---- timed region: exactly K steps, per-launch events for the roofline ----
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    # ---- timed region: exactly K steps, one event pair per launch ----
+    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -293,29 +364,32 @@ def run_gpu(args, rank: int, local_rank: int, world: int):
     # Untimed lead-in of the same launches (about half a second) so that the 100 ms clock sampler
     # sees the GPU in the loaded state the timed steps run in; the timed region follows at once.
     t_load0 = time.time()
-    lead_in = args.lead_in
-    for _ in range(lead_in):
+    for _ in range(args.lead_in):
         step()
-    evs[0].record()
     for i in range(args.steps):
+        if flush_buf is not None:
+            flush_buf.zero_()
+        ev0[i].record()
         step()
-        evs[i + 1].record()
+        ev1[i].record()
     barrier()
     t_load1 = time.time()
-    total_ms = evs[0].elapsed_time(evs[-1])
-    per_launch = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    per_launch = [a.elapsed_time(b) for a, b in zip(ev0, ev1)]
+    if flush_buf is None:
+        total_ms = ev0[0].elapsed_time(ev1[-1])  # back-to-back launches: the whole region
+    else:
+        total_ms = float(np.sum(per_launch))  # L2 flushes between steps are not part of a step
     clocks = sampler.stop(t_load0 + 0.1, t_load1) if rank == 0 else None
     _lib.raise_on_device_error()
 
     # ---- end to end through the public API from pinned host buffers ----
     e2e_steps = max(2, min(args.steps, 5))
-    host_step()
+    w["host_step"]()
     barrier()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(e2e_steps):
-        host_step()
+        w["host_step"]()
     t1.record()
     barrier()
     e2e_ms = t0.elapsed_time(t1)
@@ -326,39 +400,39 @@ def run_gpu(args, rank: int, local_rank: int, world: int):
     total_ms, e2e_ms = float(t[0]), float(t[1])
 
     if rank == 0:
-        unit = unit_for(kind)
-        value = world * info["flops"] * args.steps / (total_ms * 1e-3) / 1e12
-        e2e_val = world * info["flops"] * e2e_steps / (e2e_ms * 1e-3) / 1e12
-        avg_launch_ms = float(np.mean(per_launch))
-        achieved = info["flops"] / (avg_launch_ms * 1e-3) / 1e12
-        peak = peaks["bf16"] * RATE_VS_BF16[kind]
-        roofline = {
-            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-            "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-            "peak_source": f"{RATE_VS_BF16[kind]:g} x cuBLAS bf16 burst {peaks['bf16']} TFLOP/s ({peaks['src']})",
-            "frac_of_spec": achieved / (SPEC_BF16_TFLOPS * RATE_VS_BF16[kind]),
-            "kernel_ms": avg_launch_ms,
-        }
-        # CPU baseline: the oracle on a bounded row sample (a few seconds of host time)
-        cstep, cinfo = build_cpu_workload(args.workload, args.cpu_rows)
-        ctot, _ = time_cpu(cstep, 2, 1)
-        cpu_val = cinfo["flops"] * 2 / ctot / 1e12
-        sample = f"{cinfo['rows']} of {cinfo['M']} rows x all {cinfo['N']} columns, K={cinfo['K']}, 2 timed passes"
+        kind, unit, scale = w["kind"], w["unit"], w["scale"]
+        value = world * w["work"] * args.steps / (total_ms * 1e-3) / scale
+        e2e_val = world * w["work"] * e2e_steps / (e2e_ms * 1e-3) / scale
+        avg_ms = float(np.mean(per_launch))
+        sustained = args.lead_in >= 200  # a long identical lead-in puts the part in its power-capped steady state
+        if w["bound"] == "tensor":
+            achieved = w["work"] / (avg_ms * 1e-3) / 1e12
+            bf16_peak = peaks["bf16_sustained"] if sustained else peaks["bf16"]
+            rate = 4.0 / 3.0 if w["family"] == "attn" else RATE_VS_BF16[kind]
+            peak = bf16_peak * rate
+            why = "FP8 QK^T at 2x + BF16 PV at 1x of equal flops -> 4/3 x" if w["family"] == "attn" else f"{rate:g} x"
+            roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                        "peak_source": f"{why} cuBLAS bf16 {'sustained' if sustained else 'burst'} {bf16_peak} TFLOP/s ({peaks['src']})",
+                        "frac_of_spec": achieved / (SPEC_BF16_TFLOPS * rate), "kernel_ms": avg_ms}
+        else:
+            achieved = w["algo_bytes"] / (avg_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_bytes": w["algo_bytes"],
+                        "peak_source": f"copy bandwidth {peaks['hbm_gbs']} GB/s ({peaks['src']})", "kernel_ms": avg_ms}
+        cstep, cwork, sample = build_cpu_workload(args.workload, args.cpu_rows)
+        ctot = time_cpu(cstep, 2, 1)
+        cfg = {"workload": args.workload, **w["config"], "parallelism": "replicas only" if world > 1 else "single GPU",
+               "l2": (f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB > 126 MB L2 (no flush needed)" if flush_buf is None
+                      else f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB could stay in L2: 252 MiB written between steps, steps timed one by one"),
+               "lead_in_steps": args.lead_in}
         line = {
-            "metric": info["metric"], "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": w["metric"], "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": kind, "data": "synthetic",
-            "config": {
-                "workload": args.workload, "M": info["M"], "N": info["N"], "K": info["K"],
-                "parallelism": "replicas only" if world > 1 else "single GPU",
-                "l2": f"operands + output {info['resident_bytes'] / 2**20:.0f} MiB > 126 MB L2 (no flush needed)",
-                "lead_in_steps": lead_in,
-            },
-            "roofline": roofline,
-            "cpu_baseline": {"value": cpu_val, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
-            "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": info["h2d"], "d2h_bytes_per_step": info["d2h"], "steps": e2e_steps},
-            "gpu_launches": args.steps,
-            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"], "samples": clocks["samples"]},
+            "dtype": kind, "data": "synthetic", "config": cfg, "roofline": roofline,
+            "cpu_baseline": {"value": cwork * 2 / ctot / scale, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample + ", 2 timed passes"},
+            "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"], "steps": e2e_steps},
+            "gpu_launches": args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -373,7 +447,7 @@ def main():
     ap.add_argument("--lead-in", type=int, default=1000, help="untimed launches right before the timed region (clock sampling)")
     ap.add_argument("--workload", default="mxfp8_gemm_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="gnk", choices=["gnk", "reference"])
-    ap.add_argument("--cpu-rows", type=int, default=512, help="rows of A in the CPU sample (bounded host time)")
+    ap.add_argument("--cpu-rows", type=int, default=512, help="rows of the CPU sample (bounded host time)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -522,40 +522,40 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         if (rs_ok) {
           const int lr0 = (u / g.tiles_n) * 128, c0 = (u % g.tiles_n) * BN;
           constexpr int kPiecesPerRow = BN / 8;
-          constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread: kUnroll x world
+          // All slots of two pieces are requested before anything is added, so one memory round trip
+          // covers 2 x world 16-byte loads per thread (the loop over slots is unrolled to the maximum
+          // world size and predicated); the fp32 sums run in rank order.
+          constexpr int kUnroll = 2;
           for (int p0 = ct; p0 < 128 * kPiecesPerRow; p0 += 128 * kUnroll) {
-            float acc8[kUnroll][8];
-#pragma unroll
-            for (int q = 0; q < kUnroll; ++q)
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc8[q][e] = 0.f;
-            for (int sr = 0; sr < g.rs.world; ++sr) {
-              uint4 v[kUnroll];
-#pragma unroll
-              for (int q = 0; q < kUnroll; ++q) {
-                const int piece = p0 + q * 128;
-                const int rr = lr0 + piece / kPiecesPerRow, cc = c0 + (piece % kPiecesPerRow) * 8;
-                // L2-only loads: the lines were written by other GPUs during this kernel
-                v[q] = __ldcg(reinterpret_cast<const uint4*>(
-                    my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr) * g.N + cc));
-              }
-#pragma unroll
-              for (int q = 0; q < kUnroll; ++q) {
-                const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  acc8[q][2 * e] += __uint_as_float(w[e] << 16);
-                  acc8[q][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
-                }
-              }
-            }
+            uint4 v[kUnroll][kMaxWorld];
+            int rr[kUnroll], cc[kUnroll];
 #pragma unroll
             for (int q = 0; q < kUnroll; ++q) {
               const int piece = p0 + q * 128;
-              const int rr = lr0 + piece / kPiecesPerRow, cc = c0 + (piece % kPiecesPerRow) * 8;
-              *reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr) * g.rs.ldo + cc) =
-                  make_uint4(pack_bf16x2(acc8[q][0], acc8[q][1]), pack_bf16x2(acc8[q][2], acc8[q][3]),
-                             pack_bf16x2(acc8[q][4], acc8[q][5]), pack_bf16x2(acc8[q][6], acc8[q][7]));
+              rr[q] = lr0 + piece / kPiecesPerRow;
+              cc[q] = c0 + (piece % kPiecesPerRow) * 8;
+#pragma unroll
+              for (int sr = 0; sr < kMaxWorld; ++sr)
+                if (sr < g.rs.world)  // L2-only loads: the lines were written by other GPUs during this kernel
+                  v[q][sr] = __ldcg(reinterpret_cast<const uint4*>(
+                      my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr[q]) * g.N + cc[q]));
+            }
+#pragma unroll
+            for (int q = 0; q < kUnroll; ++q) {
+              float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+              for (int sr = 0; sr < kMaxWorld; ++sr)
+                if (sr < g.rs.world) {
+                  const uint32_t w[4] = {v[q][sr].x, v[q][sr].y, v[q][sr].z, v[q][sr].w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    acc8[2 * e] += __uint_as_float(w[e] << 16);
+                    acc8[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+                  }
+                }
+              *reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr[q]) * g.rs.ldo + cc[q]) =
+                  make_uint4(pack_bf16x2(acc8[0], acc8[1]), pack_bf16x2(acc8[2], acc8[3]), pack_bf16x2(acc8[4], acc8[5]),
+                             pack_bf16x2(acc8[6], acc8[7]));
             }
           }
         }
