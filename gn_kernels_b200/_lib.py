@@ -51,6 +51,7 @@ _SIGNATURES = {
                                  c_int64, c_int, c_int, c_uint32, _P]),
     "gnk_debug_force_tile": (c_int, [c_int]),
     "gnk_debug_staged": (c_int, [c_int]),
+    "gnk_debug_flags": (c_int, [c_int]),
     "gnk_debug_max_clusters": (c_int, [c_int]),
     "gnk_debug_trace": (c_int, [_P]),
 }

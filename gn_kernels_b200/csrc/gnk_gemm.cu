@@ -110,6 +110,7 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
 enum TileSel { T_2x256, T_1x256, T_1x128, T_1x64 };
 int g_force_tile = -1;  // test hook (gnk_debug_force_tile)
 int g_staged = -1;      // test hook (gnk_debug_staged)
+int g_dbg = 0;          // test hook (gnk_debug_flags)
 
 TileSel pick_tile(int64_t M, int64_t N, bool block_scaled) {
   if (g_force_tile >= 0) return static_cast<TileSel>(g_force_tile);
@@ -117,7 +118,7 @@ TileSel pick_tile(int64_t M, int64_t N, bool block_scaled) {
   auto ctas = [&](int64_t bm, int64_t bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
   if (ctas(256, 256) * 2 >= sms) return T_2x256;
   if (ctas(128, 256) >= sms) return T_1x256;
-  if (block_scaled || ctas(128, 128) >= sms) return T_1x128;
+  if (ctas(128, 128) >= sms) return T_1x128;
   return T_1x64;
 }
 
@@ -134,8 +135,7 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
     case T_1x256: return launch<KIND, 256, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x128: return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x64:
-      if constexpr (!kBS) return launch<KIND, 64, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
-      return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+      return launch<KIND, 64, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
   }
   return GNK_ERR_UNSUPPORTED;
 }
@@ -158,6 +158,7 @@ GemmArgs base_args(void* C, int64_t ldc, int64_t M, int64_t N, int out_elem_byte
   g.alpha = 1.f;
   g.vec_ok = aligned16(C) && ((ldc * out_elem_bytes) % 16 == 0);
   g.trace = g_trace;
+  g.dbg = g_dbg;
   return g;
 }
 
@@ -184,6 +185,12 @@ extern "C" int gnk_debug_trace(void* device_buffer) {
 // Debug: staged epilogue of the 256x256 pair tile: -1 = default per kind, 0 = direct stores, 1 = staged.
 extern "C" int gnk_debug_staged(int mode) {
   g_staged = mode;
+  return GNK_OK;
+}
+
+// Debug bits for timing experiments (bit 0: skip scale-factor copies; results are then wrong).
+extern "C" int gnk_debug_flags(int bits) {
+  g_dbg = bits;
   return GNK_OK;
 }
 

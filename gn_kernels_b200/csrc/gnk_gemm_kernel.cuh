@@ -31,6 +31,7 @@ struct GemmArgs {
   float alpha;
   int vec_ok;  // C rows 16-byte aligned: vector stores allowed
   long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
+  int dbg;           // debug bits: 1 = skip the scale-factor copies (timing experiments only, wrong results)
   // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
   // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
   // THIS GPU.  Flag words: one per owned 128 x BN unit, then a CTA ticket, then the exit counter.
@@ -379,6 +380,13 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
+        // a 64-wide tile uses half of a 128-row scale atom of B: rows 64..127 sit in TMEM columns 2 and 3
+        uint32_t sfb_half = 0;
+        if constexpr (kBS && BN == 64) {
+          int tm, tn;
+          map_tile<EPI>(t, g, tm, tn);
+          sfb_half = 2u * (tn & 1);
+        }
         for (int k = 0; k < g.k_iters; ++k) {
           const long long tr0 = g.trace ? clock64() : 0;
           if (!mbar_wait(bar_full(stage), parity, (2u << 24) | (4u << 16) | stage)) { ok = false; break; }
@@ -390,7 +398,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
           const uint64_t sfb_desc = sdesc_sf(stage_sfb(stage));
           const uint32_t empty = bar_empty(stage);
           if (leader) {
-            if constexpr (kBS) {
+            if (kBS && !(g.dbg & 1)) {
               constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per stage: 1 (mxfp8) or 4 (nvfp4)
 #pragma unroll
               for (int a = 0; a < kAtoms; ++a) {
@@ -409,11 +417,11 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
               } else if constexpr (KIND == MmaKind::MXF8F6F4) {
                 // the four K steps of a stage read bytes 0..3 of the same scale columns (scale ids in the descriptor)
                 tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc | (kk << 4) | (kk << 29), sf_tmem,
-                                    sf_tmem + C::kSfaCols, accum);
+                                    sf_tmem + C::kSfaCols + sfb_half, accum);
               } else {
                 // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
                 tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, sf_tmem + 4 * kk,
-                                    sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4, accum);
+                                    sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4 + sfb_half, accum);
               }
             }
             if constexpr (CG == 2) tc_commit_pair(empty, 3); else tc_commit<1>(empty);

@@ -212,6 +212,7 @@ int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, voi
 int gnk_debug_force_tile(int sel);
 int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default per kind, 0 direct stores, 1 staged through shared memory */
 int gnk_debug_max_clusters(int n);
+int gnk_debug_flags(int bits); /* timing experiments only: bit 0 skips scale-factor copies (wrong results) */
 int gnk_debug_trace(void* device_buffer);
 
 #ifdef __cplusplus
