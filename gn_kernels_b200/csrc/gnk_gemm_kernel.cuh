@@ -31,7 +31,7 @@ struct GemmArgs {
   float alpha;
   int vec_ok;  // C rows 16-byte aligned: vector stores allowed
   long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
-  int dbg;           // debug bits: 1 = skip the scale-factor copies (timing experiments only, wrong results)
+  int dbg;           // debug bits (timing experiments only, wrong results): 1 skip scale-factor copies, 2 reduce-scatter reducers only wait, 4 reduce-scatter stores stay local
   // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
   // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
   // THIS GPU.  Flag words: one per owned 128 x BN unit, then a CTA ticket, then the exit counter.
@@ -463,7 +463,8 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         // this rank's slot in the staging buffer of the rank that owns the row
         const int owner = row / g.rs.rows_per_owner;
         const int lrow = row - owner * g.rs.rows_per_owner;
-        rowptr = g.rs.staging[owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
+        // (debug bit 4: keep the stores on this GPU - timing experiments only, wrong results)
+        rowptr = g.rs.staging[(g.dbg & 4) ? g.rs.rank : owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
         const int lrow0 = (tm * CG + cta_rank) * 128 - owner * g.rs.rows_per_owner;
         rs_flag = g.rs.flags[owner] + (lrow0 / 128) * g.tiles_n + tn;
       } else if constexpr (EPI == EPI_I32) {
@@ -527,7 +528,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       for (int u = blockIdx.x; u < units; u += gridDim.x) {
         if (ct == 0) rs_ok = wait_flag_eq(my_flags + u, g.rs.world, g.rs.timeout_ms, (4u << 24) | (6u << 16) | (u & 0xFFFF));
         asm volatile("bar.sync 3, 128;" ::: "memory");
-        if (rs_ok) {
+        if (rs_ok && !(g.dbg & 2)) {  // (debug bit 2: wait and reset only - timing experiments)
           const int lr0 = (u / g.tiles_n) * 128, c0 = (u % g.tiles_n) * BN;
           constexpr int kPiecesPerRow = BN / 8;
           // All slots of two pieces are requested before anything is added, so one memory round trip

@@ -9,6 +9,8 @@
 // overwrite staging that a slower rank is still reducing.  Only plain peer stores, peer
 // atomics and local loads cross or follow NVLink traffic: no TMA load here names peer memory
 // and none uses cluster multicast.
+#include <cstdlib>
+
 #include "gnk_gemm_kernel.cuh"
 
 namespace gnk {
@@ -17,6 +19,15 @@ namespace {
 using namespace gnk::gemm;
 
 GNK_DEFINE_STATUS_READER(gemm_rs_status_reader)
+
+// timing experiments: GNK_RS_DEBUG=<bits> in the environment (read once)
+int rs_debug_bits() {
+  static int bits = [] {
+    const char* e = getenv("GNK_RS_DEBUG");
+    return e ? atoi(e) : 0;
+  }();
+  return bits;
+}
 
 struct RsPlan {
   int cg, bn;
@@ -154,6 +165,7 @@ extern "C" int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64
     g.rs.staging[r] = static_cast<__nv_bfloat16*>(staging[r]);
     g.rs.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
   }
+  g.dbg = rs_debug_bits();
   g.rs.out = static_cast<__nv_bfloat16*>(output);
   g.rs.ldo = ldo;
   if (p.cg == 2) return launch_rs<256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
