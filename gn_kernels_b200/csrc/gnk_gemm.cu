@@ -101,7 +101,7 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   int clusters = resident[dev];
   if (g_max_clusters > 0 && clusters > g_max_clusters) clusters = g_max_clusters;
   if (clusters > tiles) clusters = tiles;
-  kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, g);
+  kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, EpiMaps<EPI>{}, g);
   GNK_LAUNCH_OK();
   return GNK_OK;
 }

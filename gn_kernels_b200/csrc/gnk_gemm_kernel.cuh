@@ -47,6 +47,18 @@ struct GemmArgs {
   } rs;
 };
 
+// Tensor maps of the epilogue.  Only the reduce-scatter variant has any: one per owner rank, over
+// this rank's slot in that owner's staging buffer ([rows_per_owner, N] bf16, 64 x 32 boxes, 128-byte
+// swizzle), used for bulk tensor STORES of finished tiles into peer memory.
+template <int EPI>
+struct EpiMaps {
+  int unused;
+};
+template <>
+struct EpiMaps<EPI_RS> {
+  CUtensorMap slot[kMaxWorld];
+};
+
 template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16, bool STG = true>
 struct Cfg {
   using KI = KindInfo<KIND>;
@@ -245,11 +257,34 @@ __device__ __forceinline__ void flush_smem_rows(uint32_t stg, int lane, __nv_bfl
   }
 }
 
+// Staging for a bulk tensor store: the warp's 32 x BN tile as BN/64 column blocks of [32 rows][128 bytes]
+// in the 128-byte swizzle (16-byte piece index XOR row % 8), the layout a 64 x 32 box store reads.
+template <MmaKind KIND, int EPI, int BN>
+__device__ __forceinline__ void drain_to_smem_sw128(uint32_t taddr_row, int c0, int c1, const GemmArgs& g, int ncol0,
+                                                    float sa, uint32_t stg, int r) {
+  for (int c = c0; c < c1; c += 16) {
+    uint32_t raw[16];
+    tmem_ld16(taddr_row + c, raw);
+    tc_wait_ld();
+    float f[16];
+    finish_cols<KIND, EPI, 16>(raw, g, ncol0 + c, sa, f);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int piece = (c >> 3) + j;  // 16-byte piece of the row
+      const uint32_t addr = stg + (piece >> 3) * 4096 + r * 128 + (((piece & 7) ^ (r & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(f[8 * j], f[8 * j + 1])),
+                   "r"(pack_bf16x2(f[8 * j + 2], f[8 * j + 3])), "r"(pack_bf16x2(f[8 * j + 4], f[8 * j + 5])),
+                   "r"(pack_bf16x2(f[8 * j + 6], f[8 * j + 7]))
+                   : "memory");
+    }
+  }
+}
+
 template <MmaKind KIND, int BN, int CG, int EPI, bool STG = true>
 __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-                const GemmArgs g) {
+                const __grid_constant__ EpiMaps<EPI> epi_maps, const GemmArgs g) {
   using C = Cfg<KIND, BN, CG, EPI, STG>;
   constexpr bool kBS = C::KI::kBlockScaled;
   constexpr int S = C::kStages;
@@ -270,7 +305,11 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   auto bar_tempty = [&](int s) { return bar_base + 8 * (2 * S + 2 + s); };
   const uint32_t bar_partial = bar_base + 8 * (2 * S + 4);
   const uint32_t tmem_slot = bar_base + 8 * (2 * S + 5);
-  const uint32_t epi_smem = (tmem_slot + 8 + 127u) & ~127u;  // staging area of the staged epilogue (if any)
+  // staging area of the staged epilogue (if any); the bulk-store variant reads it in the 128-byte
+  // swizzle, whose pattern follows absolute address bits, hence 1024-byte alignment there (the
+  // stage buffers of the bf16 kind are multiples of 1024 bytes, so this stays inside the 2 KB slack)
+  constexpr uint32_t kEpiAlign = EPI == EPI_RS ? 1024u : 128u;
+  const uint32_t epi_smem = (tmem_slot + 8 + kEpiAlign - 1) & ~(kEpiAlign - 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -476,6 +515,8 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       // staged path: full tiles with 16-byte aligned rows (always the case for the reduce-scatter variant)
       bool staged = false;
       if constexpr (C::kStaged) staged = g.vec_ok && (ncol0 + BN <= g.N);
+      // the reduce-scatter pair tile always covers whole 256 x 256 blocks of one owner's rows
+      constexpr bool kBulkStore = EPI == EPI_RS && C::kStaged && !C::kOverlap;
       const uint32_t stg = epi_smem + warp * (32 * BN * 2);
       if constexpr (C::kOverlap) {
         // the columns shared with the other accumulator go first and are released at once
@@ -490,13 +531,32 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, p0, p1, g, ncol0, sa, stg, lane);
         else drain_cols<KIND, EPI>(taddr_row, p0, p1, g, row, ncol0, sa, rowptr);
       } else {
-        if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
+        if constexpr (kBulkStore) drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
+        else if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
         else drain_cols<KIND, EPI>(taddr_row, 0, BN, g, row, ncol0, sa, rowptr);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);
-      if constexpr (C::kStaged) {
+      if constexpr (kBulkStore) {
+        // TMEM is already released.  The warp's 32 x BN tile leaves as BN/64 bulk tensor stores into
+        // the owner's staging slot; the issuing lane waits until the writes are complete (not only
+        // until shared memory has been read) because the flag signal below publishes them.
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int row0 = (tm * CG + cta_rank) * 128 + warp * 32;
+          const int owner = row0 / g.rs.rows_per_owner;
+          const CUtensorMap* slot = &epi_maps.slot[(g.dbg & 4) ? g.rs.rank : owner];
+#pragma unroll
+          for (int cb = 0; cb < BN / 64; ++cb)
+            tma_store_2d(slot, stg + cb * 4096, ncol0 + cb * 64, row0 - owner * g.rs.rows_per_owner);
+          tma_store_commit();
+          tma_store_wait_all<0>();
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        __syncwarp();
+      } else if constexpr (C::kStaged) {
         if (staged) {
           // TMEM is already released; now the warp streams its 32 rows out, 512 contiguous bytes per instruction
           const int wrow0 = (tm * CG + cta_rank) * 128 + warp * 32;

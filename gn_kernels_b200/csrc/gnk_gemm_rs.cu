@@ -6,9 +6,11 @@
 // system-scope release.  Four extra warps per CTA on the owner wait (bounded) until a tile's
 // flag shows all ranks, add the slots in fp32 from the owner's own HBM and write the bf16
 // output rows.  The kernel ends with a cross-rank exit barrier so that the next call cannot
-// overwrite staging that a slower rank is still reducing.  Only plain peer stores, peer
-// atomics and local loads cross or follow NVLink traffic: no TMA load here names peer memory
-// and none uses cluster multicast.
+// overwrite staging that a slower rank is still reducing.  The 256-wide pair tile leaves through
+// bulk tensor STORES (shared memory -> the owner's slot, 64 x 32 boxes) whose completion the issuing
+// lane awaits before the flag is signalled; the 128-wide fallback uses plain peer stores.  Only
+// stores and atomics cross NVLink: every load is local, no TMA load names peer memory and none
+// uses cluster multicast.
 #include <cstdlib>
 
 #include "gnk_gemm_kernel.cuh"
@@ -94,7 +96,16 @@ int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g
   int clusters = resident[dev];
   const int tiles = g.tiles_m * g.tiles_n;
   if (clusters > tiles) clusters = tiles;
-  kern<<<clusters * CG, 320, C::kSmemBytes, st>>>(tm_a, tm_b, tm_a, tm_b, g);
+  // this rank's slot in every owner's staging buffer, as the target of the epilogue's bulk stores
+  EpiMaps<EPI_RS> maps;
+  for (int r = 0; r < kMaxWorld; ++r) {
+    const int o = r < g.rs.world ? r : 0;
+    __nv_bfloat16* slot = g.rs.staging[o] + static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner * N;
+    rc = make_tmap_2d(&maps.slot[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, slot, g.rs.rows_per_owner, N, N * 2, 32, 64,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != GNK_OK) return rc;
+  }
+  kern<<<clusters * CG, 320, C::kSmemBytes, st>>>(tm_a, tm_b, tm_a, tm_b, maps, g);
   GNK_LAUNCH_OK();
   return GNK_OK;
 }
