@@ -35,7 +35,7 @@ struct ElemInfo {
   static constexpr int kSfBlock = KIND == MmaKind::MXF8F6F4 ? 32 : 16;
 };
 
-template <MmaKind KIND, int BN, int CG, int EPI, bool STG = true>
+template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1>
 int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA, const uint8_t* SFB,
            GemmArgs g, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
   using C = Cfg<KIND, BN, CG, EPI, STG>;
@@ -101,7 +101,14 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   int clusters = resident[dev];
   if (g_max_clusters > 0 && clusters > g_max_clusters) clusters = g_max_clusters;
   if (clusters > tiles) clusters = tiles;
-  kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, EpiMaps<EPI>{}, g);
+  EpiMaps<EPI> maps;
+  if (C::kBulkC && g.vec_ok) {
+    rc = make_tmap_2d(&maps.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.C, M, N, g.ldc * 2, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != GNK_OK) return rc;
+  } else {
+    maps.c = tm_a;
+  }
+  kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, maps, g);
   GNK_LAUNCH_OK();
   return GNK_OK;
 }
@@ -128,10 +135,9 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
   constexpr bool kBS = KindInfo<KIND>::kBlockScaled;
   switch (pick_tile(M, N, kBS)) {
     case T_2x256:
-      // staged (coalesced) epilogue costs pipeline stages; g_staged: -1 = per-kind default, 0 = off, 1 = on
-      if (g_staged == 0 || (g_staged < 0 && kBS))
-        return launch<KIND, 256, 2, EPI, false>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
-      return launch<KIND, 256, 2, EPI, true>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+      // g_staged: 0 = direct stores from registers, anything else = bulk tensor stores through staging
+      if (g_staged == 0) return launch<KIND, 256, 2, EPI, 0>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+      return launch<KIND, 256, 2, EPI, 2>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x256: return launch<KIND, 256, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x128: return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x64:

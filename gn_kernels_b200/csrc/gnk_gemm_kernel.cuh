@@ -47,25 +47,36 @@ struct GemmArgs {
   } rs;
 };
 
-// Tensor maps of the epilogue.  Only the reduce-scatter variant has any: one per owner rank, over
+// Tensor maps of the epilogue.  The reduce-scatter variant has one per owner rank, over
 // this rank's slot in that owner's staging buffer ([rows_per_owner, N] bf16, 64 x 32 boxes, 128-byte
 // swizzle), used for bulk tensor STORES of finished tiles into peer memory.
 template <int EPI>
 struct EpiMaps {
-  int unused;
+  CUtensorMap c;  // the bf16 output [M, N], 64 x 32 boxes, 128-byte swizzle (bulk-store epilogue only)
 };
 template <>
 struct EpiMaps<EPI_RS> {
   CUtensorMap slot[kMaxWorld];
 };
+template <int EPI>
+__device__ __forceinline__ const CUtensorMap* output_map(const EpiMaps<EPI>& m) {
+  return &m.c;
+}
+template <>
+__device__ __forceinline__ const CUtensorMap* output_map<EPI_RS>(const EpiMaps<EPI_RS>& m) {
+  return &m.slot[0];  // never used: the reduce-scatter variant stores through slot[owner]
+}
 
-template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16, bool STG = true>
+template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16, int STG = 1>
 struct Cfg {
   using KI = KindInfo<KIND>;
-  // bf16 outputs of the 256-wide pair tile leave through a per-warp shared-memory staging area
-  // (32 rows x BN) so that every global store instruction writes one whole 512-byte row segment
-  static constexpr bool kStaged = STG && BN == 256 && CG == 2 && EPI != EPI_I32;
-  static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : 0;
+  // bf16 outputs of the 256-wide pair tile leave through per-warp shared-memory staging and bulk
+  // tensor stores.  Plain GEMMs (STG != 0): two 4 KB buffers per warp, one 64-column block each,
+  // so only 32 KB of pipeline space is given up.  The reduce-scatter variant stages the whole
+  // 32 x 256 piece (16 KB per warp) because it waits for completion once per tile.
+  static constexpr bool kStaged = EPI == EPI_RS && BN == 256 && CG == 2;
+  static constexpr bool kBulkC = STG != 0 && BN == 256 && CG == 2 && EPI != EPI_I32 && EPI != EPI_RS;
+  static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : kBulkC ? 4 * 2 * 4096 : 0;
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = (BN / CG) * 128;
   static constexpr int kSfAtomBytes = 128 * KI::kSfPerStage;           // one 128-row group, one stage
@@ -219,49 +230,11 @@ __device__ __forceinline__ void drain_cols(uint32_t taddr_row, int c0, int c1, c
   }
 }
 
-// Staged epilogue, step 1: columns [c0, c1) of this thread's row -> bf16 -> the warp's staging
-// area (row pitch BN*2 bytes; the 16-byte column index is XORed with the row so that both this
-// write and the row-wise read back are bank-conflict free).
-template <MmaKind KIND, int EPI, int BN>
-__device__ __forceinline__ void drain_to_smem(uint32_t taddr_row, int c0, int c1, const GemmArgs& g, int ncol0, float sa,
-                                              uint32_t stg, int r) {
-  for (int c = c0; c < c1; c += 16) {
-    uint32_t raw[16];
-    tmem_ld16(taddr_row + c, raw);
-    tc_wait_ld();
-    float f[16];
-    finish_cols<KIND, EPI, 16>(raw, g, ncol0 + c, sa, f);
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint32_t addr = stg + r * (BN * 2) + ((((c >> 3) + j) ^ r) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(f[8 * j], f[8 * j + 1])),
-                   "r"(pack_bf16x2(f[8 * j + 2], f[8 * j + 3])), "r"(pack_bf16x2(f[8 * j + 4], f[8 * j + 5])),
-                   "r"(pack_bf16x2(f[8 * j + 6], f[8 * j + 7]))
-                   : "memory");
-    }
-  }
-}
-// Staged epilogue, step 2: the warp writes its 32 rows, one full row (BN bf16 = 32 lanes x 16 bytes) per instruction.
-template <int BN>
-__device__ __forceinline__ void flush_smem_rows(uint32_t stg, int lane, __nv_bfloat16* row0_ptr, int64_t row_pitch,
-                                                int rows_valid) {
-  static_assert(BN == 256, "one 16-byte piece per lane");
-#pragma unroll 4
-  for (int rr = 0; rr < 32; ++rr) {
-    uint32_t a, b, c, d;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-                 : "r"(stg + rr * (BN * 2) + ((lane ^ rr) << 4))
-                 : "memory");
-    if (rr < rows_valid) *reinterpret_cast<uint4*>(row0_ptr + rr * row_pitch + lane * 8) = make_uint4(a, b, c, d);
-  }
-}
-
 // Staging for a bulk tensor store: the warp's 32 x BN tile as BN/64 column blocks of [32 rows][128 bytes]
 // in the 128-byte swizzle (16-byte piece index XOR row % 8), the layout a 64 x 32 box store reads.
 template <MmaKind KIND, int EPI, int BN>
 __device__ __forceinline__ void drain_to_smem_sw128(uint32_t taddr_row, int c0, int c1, const GemmArgs& g, int ncol0,
-                                                    float sa, uint32_t stg, int r) {
+                                                    float sa, uint32_t stg, int r, uint32_t blk_stride = 4096) {
   for (int c = c0; c < c1; c += 16) {
     uint32_t raw[16];
     tmem_ld16(taddr_row + c, raw);
@@ -271,7 +244,7 @@ __device__ __forceinline__ void drain_to_smem_sw128(uint32_t taddr_row, int c0, 
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int piece = (c >> 3) + j;  // 16-byte piece of the row
-      const uint32_t addr = stg + (piece >> 3) * 4096 + r * 128 + (((piece & 7) ^ (r & 7)) << 4);
+      const uint32_t addr = stg + (piece >> 3) * blk_stride + r * 128 + (((piece & 7) ^ (r & 7)) << 4);
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(f[8 * j], f[8 * j + 1])),
                    "r"(pack_bf16x2(f[8 * j + 2], f[8 * j + 3])), "r"(pack_bf16x2(f[8 * j + 4], f[8 * j + 5])),
                    "r"(pack_bf16x2(f[8 * j + 6], f[8 * j + 7]))
@@ -280,7 +253,7 @@ __device__ __forceinline__ void drain_to_smem_sw128(uint32_t taddr_row, int c0, 
   }
 }
 
-template <MmaKind KIND, int BN, int CG, int EPI, bool STG = true>
+template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1>
 __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -293,9 +266,12 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // [stage][A | B | SFA | SFB]; A and B stage buffers stay 1024-byte aligned (sizes are multiples of 1024... SF after them)
-  auto stage_a = [&](int s) { return smem_base + s * (C::kABytes + C::kBBytes); };
+  // the bulk-store staging (read by TMA in the 128-byte swizzle, hence 1024-byte aligned) comes first
+  constexpr bool kEpiFirst = C::kBulkC || (EPI == EPI_RS && C::kStaged);
+  const uint32_t ab_base = smem_base + (kEpiFirst ? C::kEpiBytes : 0);
+  auto stage_a = [&](int s) { return ab_base + s * (C::kABytes + C::kBBytes); };
   auto stage_b = [&](int s) { return stage_a(s) + C::kABytes; };
-  const uint32_t sf_base = smem_base + S * (C::kABytes + C::kBBytes);
+  const uint32_t sf_base = ab_base + S * (C::kABytes + C::kBBytes);
   auto stage_sfa = [&](int s) { return sf_base + s * (C::kSfaBytes + C::kSfbBytes); };
   auto stage_sfb = [&](int s) { return stage_sfa(s) + C::kSfaBytes; };
   const uint32_t bar_base = sf_base + S * (C::kSfaBytes + C::kSfbBytes);
@@ -305,11 +281,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   auto bar_tempty = [&](int s) { return bar_base + 8 * (2 * S + 2 + s); };
   const uint32_t bar_partial = bar_base + 8 * (2 * S + 4);
   const uint32_t tmem_slot = bar_base + 8 * (2 * S + 5);
-  // staging area of the staged epilogue (if any); the bulk-store variant reads it in the 128-byte
-  // swizzle, whose pattern follows absolute address bits, hence 1024-byte alignment there (the
-  // stage buffers of the bf16 kind are multiples of 1024 bytes, so this stays inside the 2 KB slack)
-  constexpr uint32_t kEpiAlign = EPI == EPI_RS ? 1024u : 128u;
-  const uint32_t epi_smem = (tmem_slot + 8 + kEpiAlign - 1) & ~(kEpiAlign - 1);
+  const uint32_t epi_smem = kEpiFirst ? smem_base : (tmem_slot + 8 + 127u) & ~127u;  // epilogue staging (if any)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -512,32 +484,67 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         rowptr = static_cast<__nv_bfloat16*>(g.C) + static_cast<int64_t>(row) * g.ldc;
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + acc * C::kAccStride;
-      // staged path: full tiles with 16-byte aligned rows (always the case for the reduce-scatter variant)
+      // bulk-store path: full-width tiles of an output with 16-byte aligned rows
       bool staged = false;
-      if constexpr (C::kStaged) staged = g.vec_ok && (ncol0 + BN <= g.N);
       // the reduce-scatter pair tile always covers whole 256 x 256 blocks of one owner's rows
       constexpr bool kBulkStore = EPI == EPI_RS && C::kStaged && !C::kOverlap;
-      const uint32_t stg = epi_smem + warp * (32 * BN * 2);
+      const uint32_t stg = epi_smem + warp * (C::kBulkC ? 2 * 4096 : 32 * BN * 2);
+      if constexpr (C::kBulkC) staged = g.vec_ok && (ncol0 + BN <= g.N);
+      if (C::kBulkC && staged) {
+        // Four 64-column blocks, each: wait until the buffer's previous store has read it, drain the
+        // block into it (swizzled), hand it to a bulk tensor store (rows beyond M are clipped).  With
+        // overlapping accumulators the block holding the shared columns goes first.
+        const int row0 = (tm * CG + cta_rank) * 128 + warp * 32;
+        const int first = (C::kOverlap && acc == 0) ? 3 : 0;
+#pragma unroll 1
+        for (int i = 0; i < 4; ++i) {
+          const int cb = (first + i) & 3;
+          const uint32_t buf = stg + (i & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          if (C::kOverlap && i == 0) {
+            const int o0 = acc == 0 ? C::kAccStride : 0;
+            const int o1 = o0 + C::kOverlapCols;
+            drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, o0, o1, g, ncol0, sa, buf - cb * 4096, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(partial);
+            if (acc == 0) drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, 192, o0, g, ncol0, sa, buf - cb * 4096, lane);
+            else drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, o1, 64, g, ncol0, sa, buf - cb * 4096, lane);
+          } else {
+            drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, cb * 64, cb * 64 + 64, g, ncol0, sa, buf - cb * 4096, lane);
+          }
+          if (i == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(output_map<EPI>(epi_maps), buf, ncol0 + cb * 64, row0);
+            tma_store_commit();
+          }
+        }
+      } else {
       if constexpr (C::kOverlap) {
         // the columns shared with the other accumulator go first and are released at once
         const int o0 = acc == 0 ? C::kAccStride : 0;
         const int o1 = o0 + C::kOverlapCols;
-        if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, o0, o1, g, ncol0, sa, stg, lane);
-        else drain_cols<KIND, EPI>(taddr_row, o0, o1, g, row, ncol0, sa, rowptr);
+        drain_cols<KIND, EPI>(taddr_row, o0, o1, g, row, ncol0, sa, rowptr);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(partial);
         const int p0 = acc == 0 ? 0 : o1, p1 = acc == 0 ? o0 : BN;
-        if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, p0, p1, g, ncol0, sa, stg, lane);
-        else drain_cols<KIND, EPI>(taddr_row, p0, p1, g, row, ncol0, sa, rowptr);
+        drain_cols<KIND, EPI>(taddr_row, p0, p1, g, row, ncol0, sa, rowptr);
       } else {
         if constexpr (kBulkStore) drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
-        else if (staged) drain_to_smem<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
         else drain_cols<KIND, EPI>(taddr_row, 0, BN, g, row, ncol0, sa, rowptr);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);
+      }
       if constexpr (kBulkStore) {
         // TMEM is already released.  The warp's 32 x BN tile leaves as BN/64 bulk tensor stores into
         // the owner's staging slot; the issuing lane waits until the writes are complete (not only
@@ -556,17 +563,6 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         __syncwarp();
-      } else if constexpr (C::kStaged) {
-        if (staged) {
-          // TMEM is already released; now the warp streams its 32 rows out, 512 contiguous bytes per instruction
-          const int wrow0 = (tm * CG + cta_rank) * 128 + warp * 32;
-          // lane 0 holds the pointer of the warp's first row; the rows follow at a fixed pitch
-          __nv_bfloat16* first =
-              reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(rowptr), 0)) + ncol0;
-          const int64_t pitch = EPI == EPI_RS ? static_cast<int64_t>(g.N) : g.ldc;
-          flush_smem_rows<BN>(stg, lane, first, pitch, min(32, g.M - wrow0));
-          __syncwarp();
-        }
       }
       if constexpr (EPI == EPI_RS) {
         // the tile is in the owner's memory once every thread's stores are ordered before the signal
@@ -576,6 +572,11 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       }
       acc ^= 1;
       if (acc == 0) parity ^= 1;
+    }
+    // shared memory must outlive the bulk stores that still read it
+    if constexpr (C::kBulkC) {
+      if (lane == 0) tma_store_wait_all<0>();
+      __syncwarp();
     }
   } else {
     // ------------------------------ reducer (warps 6-9, reduce-scatter variant only) ------------------------------

@@ -210,7 +210,7 @@ int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, voi
  * cap the persistent grid (0 = no cap), record per-stage clock stamps of CTAs 0 and 1 into a device
  * buffer of 2*2*256*3 int64 (NULL = off).  Process-wide; for tests and profiling only. */
 int gnk_debug_force_tile(int sel);
-int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default per kind, 0 direct stores, 1 staged through shared memory */
+int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default (staged), 0 direct stores from registers, 1 bulk tensor stores through shared-memory staging */
 int gnk_debug_max_clusters(int n);
 int gnk_debug_flags(int bits); /* timing experiments only: bit 0 skips scale-factor copies (wrong results) */
 int gnk_debug_trace(void* device_buffer);

@@ -34,6 +34,7 @@ def _tile_reset_and_status():
 
     yield
     _lib.lib().gnk_debug_force_tile(-1)
+    _lib.lib().gnk_debug_staged(-1)
     _lib.raise_on_device_error()
 
 
@@ -186,6 +187,43 @@ def test_nvfp4(gk, tile, M, N, K):
 def _sampled_rows(M, n=64, seed=0):
     g = torch.Generator().manual_seed(seed)
     return torch.sort(torch.randperm(M, generator=g)[:n]).values
+
+
+@pytest.mark.parametrize("kind", ["bf16", "int8", "fp8", "mxfp8", "nvfp4"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (384, 512, 1024), (1000, 1024, 512), (2048, 2304, 4096)])
+def test_pair_tile_epilogue_modes(gk, kind, M, N, K):
+    """The 256 x 256 pair tile writes bf16 through bulk tensor stores from swizzled staging (default)
+    or straight from registers; both must give the same bits (ragged M, many tiles per cluster)."""
+    from gn_kernels_b200 import _lib
+
+    force(0)
+    A = randn_bf16((M, K), 31)
+    Bt = randn_bf16((N, K), 32)
+    if kind == "bf16":
+        run = lambda: gk.triton_mm(A, Bt.T)
+    elif kind == "int8":
+        Ai, Bi = rand_i8((M, K), 33).cuda(), rand_i8((N, K), 34).cuda()
+        sa, sb = torch.rand(M, 1, device="cuda") + 0.5, torch.rand(1, N, device="cuda") + 0.5
+        bias = torch.randn(N, device="cuda")
+        run = lambda: gk.triton_mm(Ai, Bi.T, bias, scale_A=sa, scale_B=sb)
+    elif kind == "fp8":
+        Af, Bf = A.to(torch.float8_e4m3fn), Bt.to(torch.float8_e4m3fn)
+        sa, sb = torch.rand(M, 1, device="cuda") + 0.5, torch.rand(1, N, device="cuda") + 0.5
+        run = lambda: gk.triton_mm(Af, Bf.T, scale_A=sa, scale_B=sb)
+    elif kind == "mxfp8":
+        Aq, sfa = gk.quantize_mx(A, torch.float8_e4m3fn, swizzled_scales=True)
+        Bq, sfb = gk.quantize_mx(Bt, torch.float8_e4m3fn, swizzled_scales=True)
+        run = lambda: gk.cutedsl.sm100.sm100_mm_mxfp8.mm(Aq, Bq, sfa, sfb)
+    else:
+        ts = gk.ops.absmax(A, 2688.0)
+        Aq, sfa = gk.quantize_nvfp4_triton(A, ts)
+        Bq, sfb = gk.quantize_nvfp4_triton(Bt, ts)
+        run = lambda: gk.cutedsl.sm100.sm100_mm_nvfp4.mm(Aq, Bq, sfa, sfb, float(ts) ** 2)
+    outs = []
+    for mode in (0, 1):
+        _lib.lib().gnk_debug_staged(mode)
+        outs.append(run().clone())
+    assert torch.equal(outs[0], outs[1])
 
 
 @pytest.mark.parametrize("kind", ["int8", "mxfp8", "nvfp4", "bf16"])
