@@ -44,6 +44,12 @@ struct GemmArgs {
     unsigned int* flags[kMaxWorld];
     __nv_bfloat16* out;
     int64_t ldo;
+    // Pull variant: the multicast address of the ranks' [M, N] partial buffers (staging[] are then the
+    // same buffers seen per rank).  Null selects the push variant.
+    const __nv_bfloat16* mc_partial;
+    // debug: 8 words per CTA (globaltimer ns): start, epilogue end, reducer end, reducer wait total,
+    // MMA end, epilogue store+signal total, epilogue wait-for-accumulator total (null = off)
+    unsigned long long* trace;
   } rs;
 };
 
@@ -57,6 +63,7 @@ struct EpiMaps {
 template <>
 struct EpiMaps<EPI_RS> {
   CUtensorMap slot[kMaxWorld];
+  CUtensorMap local;  // pull variant: this rank's own [M, N] partial
 };
 template <int EPI>
 __device__ __forceinline__ const CUtensorMap* output_map(const EpiMaps<EPI>& m) {
@@ -138,6 +145,28 @@ template <int EPI>
 __device__ __forceinline__ void map_tile(int t, const GemmArgs& g, int& tm, int& tn) {
   if constexpr (EPI == EPI_RS) tile_coords_rs(t, g, tm, tn);
   else tile_coords(t, g.tiles_m, g.tiles_n, tm, tn);
+}
+
+// Streaming accesses of the reducer: every staging line is read once and every output line written
+// once, so both are marked evict-first in L2 and leave the GEMM operands (which are re-read by many
+// tiles) in place.  The load stays L2-only (.cg): the lines were written by other GPUs.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint4 ld_cg_hint(const uint4* ptr, uint64_t pol) {
+  uint4 v;
+  asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr), "l"(pol)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_hint(uint4* ptr, uint4 v, uint64_t pol) {
+  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w), "l"(pol)
+               : "memory");
 }
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -230,6 +259,74 @@ __device__ __forceinline__ void drain_cols(uint32_t taddr_row, int c0, int c1, c
   }
 }
 
+// Reducer: one chunk of PB * 128 / (BN / 8) rows x BN columns of this rank's output.  Each of the 128
+// reducer threads owns PB 16-byte pieces; the loads of all slots of all its pieces are in flight
+// together (PB * world <= 16), the fp32 sums run in rank order, the result is rounded to bf16 once.
+template <int BN, int PB>
+__device__ __forceinline__ void reduce_chunk(const GemmArgs& g, const __nv_bfloat16* my_stage, int lr0, int c0, int ct,
+                                             uint64_t stream_pol) {
+  constexpr int kPiecesPerRow = BN / 8;
+  constexpr int kSlots = 16 / PB;  // most ranks this instantiation serves
+  uint4 v[PB][kSlots];
+  int rr[PB], cc[PB];
+#pragma unroll
+  for (int q = 0; q < PB; ++q) {
+    const int piece = ct + q * 128;
+    rr[q] = lr0 + piece / kPiecesPerRow;
+    cc[q] = c0 + (piece % kPiecesPerRow) * 8;
+#pragma unroll
+    for (int sr = 0; sr < kSlots; ++sr)
+      if (sr < g.rs.world) {  // L2-only loads: the lines were written by other GPUs during this kernel
+        const uint4* src = reinterpret_cast<const uint4*>(
+            my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr[q]) * g.N + cc[q]);
+        v[q][sr] = ld_cg_hint(src, stream_pol);
+      }
+  }
+#pragma unroll
+  for (int q = 0; q < PB; ++q) {
+    float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int sr = 0; sr < kSlots; ++sr)
+      if (sr < g.rs.world) {
+        const uint32_t w[4] = {v[q][sr].x, v[q][sr].y, v[q][sr].z, v[q][sr].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc8[2 * e] += __uint_as_float(w[e] << 16);
+          acc8[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+        }
+      }
+    st_hint(reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr[q]) * g.rs.ldo + cc[q]),
+            make_uint4(pack_bf16x2(acc8[0], acc8[1]), pack_bf16x2(acc8[2], acc8[3]), pack_bf16x2(acc8[4], acc8[5]),
+                       pack_bf16x2(acc8[6], acc8[7])),
+            stream_pol);
+  }
+}
+
+// Pull variant of the reducer: the same chunk, but every 16-byte piece is ONE load from the multicast
+// address of the ranks' partial buffers; NVSwitch fetches the piece from every rank, adds the bf16
+// values in fp32 and returns the rounded sum, so only the reduced data enters this SM.
+template <int BN, int PB>
+__device__ __forceinline__ void reduce_chunk_multimem(const GemmArgs& g, int lr0, int c0, int ct, uint64_t stream_pol) {
+  constexpr int kPiecesPerRow = BN / 8;
+  uint4 v[PB];
+  int rr[PB], cc[PB];
+#pragma unroll
+  for (int q = 0; q < PB; ++q) {
+    const int piece = ct + q * 128;
+    rr[q] = lr0 + piece / kPiecesPerRow;
+    cc[q] = c0 + (piece % kPiecesPerRow) * 8;
+    const __nv_bfloat16* src =
+        g.rs.mc_partial + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + rr[q]) * g.N + cc[q];
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[q].x), "=r"(v[q].y), "=r"(v[q].z), "=r"(v[q].w)
+                 : "l"(src)
+                 : "memory");
+  }
+#pragma unroll
+  for (int q = 0; q < PB; ++q)
+    st_hint(reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr[q]) * g.rs.ldo + cc[q]), v[q], stream_pol);
+}
+
 // Staging for a bulk tensor store: the warp's 32 x BN tile as BN/64 column blocks of [32 rows][128 bytes]
 // in the 128-byte swizzle (16-byte piece index XOR row % 8), the layout a 64 x 32 box store reads.
 template <MmaKind KIND, int EPI, int BN>
@@ -320,6 +417,13 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  unsigned long long* rs_tr = nullptr;
+  if constexpr (EPI == EPI_RS) {
+    if (g.rs.trace) {
+      rs_tr = g.rs.trace + blockIdx.x * 8;
+      if (threadIdx.x == 0) rs_tr[0] = globaltimer_ns();
+    }
+  }
 
   // Producer and MMA warps run their loops warp-uniformly (all 32 lanes wait on the barriers and
   // compute addresses and descriptors, which keeps those values in uniform registers); one
@@ -453,8 +557,11 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         acc ^= 1;
         if (acc == 0) acc_parity ^= 1;
       }
+      if (rs_tr && leader) rs_tr[4] = globaltimer_ns();
     }
   } else if (warp < 4) {
+    unsigned long long tr_store = 0, tr_wait = 0;
+    unsigned int* pending_flag = nullptr;  // lane 0: flag of the piece whose bulk stores are still in flight
     // ------------------------------ epilogue (warps 0-3) ------------------------------
     uint32_t acc = 0, parity = 0;
     const uint32_t tempty0 = CG == 2 ? map_to_cta(bar_tempty(0), 0) : bar_tempty(0);
@@ -463,7 +570,20 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
       int tm, tn;
       map_tile<EPI>(t, g, tm, tn);
+      const unsigned long long trw0 = rs_tr ? globaltimer_ns() : 0;
       if (!mbar_wait(bar_tfull(acc), parity, (3u << 24) | (5u << 16) | acc)) { ok = false; break; }
+      if (rs_tr) tr_wait += globaltimer_ns() - trw0;
+      if constexpr (EPI == EPI_RS) {
+        // Signal the warp's previous piece: by now its bulk stores have long completed, so this
+        // wait returns at once; it also frees the staging area for this tile.
+        if (lane == 0 && pending_flag) {
+          tma_store_wait_all<0>();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          red_release_sys_add(pending_flag, 1u);
+          pending_flag = nullptr;
+        }
+        __syncwarp();
+      }
       tc_fence_after();
       const int row = (tm * CG + cta_rank) * 128 + warp * 32 + lane;
       const int ncol0 = tn * BN;
@@ -475,7 +595,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         const int owner = row / g.rs.rows_per_owner;
         const int lrow = row - owner * g.rs.rows_per_owner;
         // (debug bit 4: keep the stores on this GPU - timing experiments only, wrong results)
-        rowptr = g.rs.staging[(g.dbg & 4) ? g.rs.rank : owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
+        if (g.rs.mc_partial)  // pull variant: the row's place in this rank's own [M, N] partial
+          rowptr = g.rs.staging[g.rs.rank] + static_cast<int64_t>(row) * g.N;
+        else
+          rowptr = g.rs.staging[(g.dbg & 4) ? g.rs.rank : owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
         const int lrow0 = (tm * CG + cta_rank) * 128 - owner * g.rs.rows_per_owner;
         rs_flag = g.rs.flags[owner] + (lrow0 / 128) * g.tiles_n + tn;
       } else if constexpr (EPI == EPI_I32) {
@@ -545,33 +668,52 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);
       }
+      const unsigned long long trs0 = rs_tr ? globaltimer_ns() : 0;
       if constexpr (kBulkStore) {
-        // TMEM is already released.  The warp's 32 x BN tile leaves as BN/64 bulk tensor stores into
-        // the owner's staging slot; the issuing lane waits until the writes are complete (not only
-        // until shared memory has been read) because the flag signal below publishes them.
+        // TMEM is already released.  The warp's 32 x BN piece leaves as BN/64 bulk tensor stores (into
+        // the owner's staging slot, or into this rank's own partial in the pull variant).  Its flag
+        // signal needs the writes complete, not only shared memory read; that wait is deferred to the
+        // start of the warp's next tile (see above), when it no longer costs anything.
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
           const int row0 = (tm * CG + cta_rank) * 128 + warp * 32;
           const int owner = row0 / g.rs.rows_per_owner;
-          const CUtensorMap* slot = &epi_maps.slot[(g.dbg & 4) ? g.rs.rank : owner];
+          const int dst = (g.dbg & 4) ? g.rs.rank : owner;
+          if (g.rs.mc_partial) {
 #pragma unroll
-          for (int cb = 0; cb < BN / 64; ++cb)
-            tma_store_2d(slot, stg + cb * 4096, ncol0 + cb * 64, row0 - owner * g.rs.rows_per_owner);
+            for (int cb = 0; cb < BN / 64; ++cb) tma_store_2d(&epi_maps.local, stg + cb * 4096, ncol0 + cb * 64, row0);
+          } else {
+#pragma unroll
+            for (int cb = 0; cb < BN / 64; ++cb)
+              tma_store_2d(&epi_maps.slot[dst], stg + cb * 4096, ncol0 + cb * 64, row0 - owner * g.rs.rows_per_owner);
+          }
           tma_store_commit();
-          tma_store_wait_all<0>();
-          asm volatile("fence.proxy.async;" ::: "memory");
+          pending_flag = rs_flag;
         }
         __syncwarp();
-      }
-      if constexpr (EPI == EPI_RS) {
-        // the tile is in the owner's memory once every thread's stores are ordered before the signal
+      } else if constexpr (EPI == EPI_RS) {
+        // plain stores by every lane: each lane orders its own, then one signal per warp
         __threadfence_system();
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (threadIdx.x == 0) red_release_sys_add(rs_flag, 1u);
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(rs_flag, 1u);
       }
+      if (rs_tr) tr_store += globaltimer_ns() - trs0;
       acc ^= 1;
       if (acc == 0) parity ^= 1;
+    }
+    if constexpr (EPI == EPI_RS) {
+      if (lane == 0 && pending_flag) {  // the warp's last tile
+        tma_store_wait_all<0>();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        red_release_sys_add(pending_flag, 1u);
+      }
+      __syncwarp();
+    }
+    if (rs_tr && threadIdx.x == 0) {
+      rs_tr[1] = globaltimer_ns();
+      rs_tr[5] = tr_store;
+      rs_tr[6] = tr_wait;
     }
     // shared memory must outlive the bulk stores that still read it
     if constexpr (C::kBulkC) {
@@ -585,52 +727,57 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;  // 128 x BN units this rank owns
       unsigned int* my_flags = g.rs.flags[g.rs.rank];
       const __nv_bfloat16* my_stage = g.rs.staging[g.rs.rank];
+      const uint64_t stream_pol = l2_evict_first_policy();
       __shared__ int rs_ok;
-      for (int u = blockIdx.x; u < units; u += gridDim.x) {
-        if (ct == 0) rs_ok = wait_flag_eq(my_flags + u, g.rs.world, g.rs.timeout_ms, (4u << 24) | (6u << 16) | (u & 0xFFFF));
+      // Work item = (unit, span of row chunks), in the order in which the ranks produce the owner's
+      // tiles, so a CTA waits for its items roughly in arrival order.
+      //  pull variant: a chunk is one batch of 8 multicast loads per thread (32 rows of a 256-wide
+      //    unit) and every chunk is an item of its own, so the chunks of a unit go to different CTAs
+      //    and every SM takes part when the last tiles of all ranks arrive together;
+      //  push variant: a chunk is one batch of 2 pieces x world slots per thread and one item covers
+      //    the whole unit (the slots are read through this SM's L2 port, which the operand loads of
+      //    the main loop already keep busy: a more aggressive reducer only slows the GEMM down).
+      const bool pull = g.rs.mc_partial != nullptr;
+      const int pb = pull ? 8 : 2;  // 16-byte pieces per thread and batch
+      const int chunk_rows = pb * 128 / (BN / 8);
+      const int chunks = 128 / chunk_rows;
+      const int span = pull ? 1 : chunks;  // chunks per item
+      const int parts = chunks / span;     // items per unit
+      const int items = units * parts;
+      unsigned int* done = my_flags + units;  // items finished per unit
+      unsigned long long red_wait = 0;
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int q = item / (CG * parts), rem = item - q * (CG * parts);
+        int lm, tn;
+        rs_local_tile(q, g.rs.tiles_per_owner, g.tiles_n, g.rs.world, lm, tn);
+        const int rb = lm * CG + rem / parts;  // 128-row block inside the owner's rows
+        const int u = rb * g.tiles_n + tn;
+        const int c0 = tn * BN;
+        if (ct == 0) {
+          const unsigned long long w0 = rs_tr ? globaltimer_ns() : 0;
+          // every rank's four epilogue warps signal their 32-row pieces of the unit separately
+          rs_ok = wait_flag_eq(my_flags + u, 4u * g.rs.world, g.rs.timeout_ms, (4u << 24) | (6u << 16) | (u & 0xFFFF));
+          if (rs_tr) red_wait += globaltimer_ns() - w0;
+        }
         asm volatile("bar.sync 3, 128;" ::: "memory");
         if (rs_ok && !(g.dbg & 2)) {  // (debug bit 2: wait and reset only - timing experiments)
-          const int lr0 = (u / g.tiles_n) * 128, c0 = (u % g.tiles_n) * BN;
-          constexpr int kPiecesPerRow = BN / 8;
-          // All slots of two pieces are requested before anything is added, so one memory round trip
-          // covers 2 x world 16-byte loads per thread (the loop over slots is unrolled to the maximum
-          // world size and predicated); the fp32 sums run in rank order.
-          constexpr int kUnroll = 2;
-          for (int p0 = ct; p0 < 128 * kPiecesPerRow; p0 += 128 * kUnroll) {
-            uint4 v[kUnroll][kMaxWorld];
-            int rr[kUnroll], cc[kUnroll];
-#pragma unroll
-            for (int q = 0; q < kUnroll; ++q) {
-              const int piece = p0 + q * 128;
-              rr[q] = lr0 + piece / kPiecesPerRow;
-              cc[q] = c0 + (piece % kPiecesPerRow) * 8;
-#pragma unroll
-              for (int sr = 0; sr < kMaxWorld; ++sr)
-                if (sr < g.rs.world)  // L2-only loads: the lines were written by other GPUs during this kernel
-                  v[q][sr] = __ldcg(reinterpret_cast<const uint4*>(
-                      my_stage + (static_cast<int64_t>(sr) * g.rs.rows_per_owner + rr[q]) * g.N + cc[q]));
-            }
-#pragma unroll
-            for (int q = 0; q < kUnroll; ++q) {
-              float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-              for (int sr = 0; sr < kMaxWorld; ++sr)
-                if (sr < g.rs.world) {
-                  const uint32_t w[4] = {v[q][sr].x, v[q][sr].y, v[q][sr].z, v[q][sr].w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    acc8[2 * e] += __uint_as_float(w[e] << 16);
-                    acc8[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
-                  }
-                }
-              *reinterpret_cast<uint4*>(g.rs.out + static_cast<int64_t>(rr[q]) * g.rs.ldo + cc[q]) =
-                  make_uint4(pack_bf16x2(acc8[0], acc8[1]), pack_bf16x2(acc8[2], acc8[3]), pack_bf16x2(acc8[4], acc8[5]),
-                             pack_bf16x2(acc8[6], acc8[7]));
-            }
+          for (int c = 0; c < span; ++c) {
+            const int lr0 = rb * 128 + ((rem % parts) * span + c) * chunk_rows;
+            if (pull) reduce_chunk_multimem<BN, 8>(g, lr0, c0, ct, stream_pol);
+            else reduce_chunk<BN, 2>(g, my_stage, lr0, c0, ct, stream_pol);
           }
         }
         asm volatile("bar.sync 3, 128;" ::: "memory");
-        if (ct == 0) my_flags[u] = 0u;  // ready for the next call (peers cannot signal again before the exit barrier)
+        // the last item of a unit clears its words for the next call (peers cannot signal again
+        // before the exit barrier)
+        if (ct == 0 && rs_ok && atomicAdd(done + u, 1u) == static_cast<unsigned int>(parts - 1)) {
+          my_flags[u] = 0u;
+          done[u] = 0u;
+        }
+      }
+      if (rs_tr && ct == 0) {
+        rs_tr[2] = globaltimer_ns();
+        rs_tr[3] = red_wait;
       }
     }
   }
@@ -650,14 +797,15 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;
       unsigned int* my_flags = g.rs.flags[g.rs.rank];
       __threadfence();
-      const unsigned int ticket = atomicAdd(my_flags + units, 1u);
+      // flag words: [units] arrivals, [units] finished chunks, CTA ticket, exit barrier
+      const unsigned int ticket = atomicAdd(my_flags + 2 * units, 1u);
       if (ticket == gridDim.x - 1) {
-        my_flags[units] = 0u;
+        my_flags[2 * units] = 0u;
         __threadfence_system();
         for (int p = 0; p < g.rs.world; ++p)
-          if (p != g.rs.rank) red_release_sys_add(g.rs.flags[p] + units + 1, 1u);
-        if (wait_flag_eq(my_flags + units + 1, g.rs.world - 1, g.rs.timeout_ms, (4u << 24) | (7u << 16)))
-          my_flags[units + 1] = 0u;
+          if (p != g.rs.rank) red_release_sys_add(g.rs.flags[p] + 2 * units + 1, 1u);
+        if (wait_flag_eq(my_flags + 2 * units + 1, g.rs.world - 1, g.rs.timeout_ms, (4u << 24) | (7u << 16)))
+          my_flags[2 * units + 1] = 0u;
       }
     }
   }

@@ -11,6 +11,14 @@
 // lane awaits before the flag is signalled; the 128-wide fallback uses plain peer stores.  Only
 // stores and atomics cross NVLink: every load is local, no TMA load names peer memory and none
 // uses cluster multicast.
+//
+// Pull variant (gnk_gemm_rs_bf16_pull, for buffers that also have an NVLink multicast address):
+// a finished tile stays in the rank's OWN [M, N] partial; only the flag update crosses NVLink.  The
+// owner's reducer warps read each 16-byte piece once through the multicast address with
+// multimem.ld_reduce (NVSwitch fetches it from every rank and adds in fp32), so an SM receives
+// only the reduced data: world times less than the push variant's slot reads, which compete
+// with the main loop's operand loads for the SM's L2 port.
+#include <cstdio>
 #include <cstdlib>
 
 #include "gnk_gemm_kernel.cuh"
@@ -105,8 +113,41 @@ int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g
                       CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != GNK_OK) return rc;
   }
+  // pull variant: finished tiles go to this rank's own [M, N] partial
+  rc = make_tmap_2d(&maps.local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.rs.staging[g.rs.rank], M, N, N * 2, 32, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != GNK_OK) return rc;
+  // timing experiments: GNK_RS_TRACE=1 prints a per-call timeline summary (synchronises the stream)
+  static const bool trace_on = getenv("GNK_RS_TRACE") != nullptr;
+  static unsigned long long* trace_dev[64];
+  if (trace_on) {
+    if (!trace_dev[dev]) GNK_CUDA_OK(cudaMalloc(&trace_dev[dev], 8 * sizeof(unsigned long long) * 1024));
+    GNK_CUDA_OK(cudaMemsetAsync(trace_dev[dev], 0, 8 * sizeof(unsigned long long) * 1024, st));
+    g.rs.trace = trace_dev[dev];
+  }
   kern<<<clusters * CG, 320, C::kSmemBytes, st>>>(tm_a, tm_b, tm_a, tm_b, maps, g);
   GNK_LAUNCH_OK();
+  if (trace_on) {
+    static unsigned long long h[8 * 1024];
+    GNK_CUDA_OK(cudaStreamSynchronize(st));
+    GNK_CUDA_OK(cudaMemcpy(h, trace_dev[dev], sizeof(h), cudaMemcpyDeviceToHost));
+    const int n = clusters * CG;
+    unsigned long long t0 = ~0ull;
+    for (int b = 0; b < n; ++b)
+      if (h[b * 8] && h[b * 8] < t0) t0 = h[b * 8];
+    double mx[8] = {0}, sum[8] = {0};
+    for (int b = 0; b < n; ++b)
+      for (int k = 0; k < 8; ++k) {
+        const double v = (k == 3 || k == 5 || k == 6) ? h[b * 8 + k] * 1e-3 : (h[b * 8 + k] ? (h[b * 8 + k] - t0) * 1e-3 : 0.0);
+        sum[k] += v;
+        if (v > mx[k]) mx[k] = v;
+      }
+    fprintf(stderr,
+            "RS_TRACE rank %d us: start max %.1f | mma end mean %.1f max %.1f | epi end mean %.1f max %.1f | red end mean "
+            "%.1f max %.1f | red wait mean %.1f | epi store+signal mean %.1f | epi wait-acc mean %.1f\n",
+            g.rs.rank, mx[0], sum[4] / (n / CG), mx[4], sum[1] / n, mx[1], sum[2] / n, mx[2], sum[3] / n, sum[5] / n,
+            sum[6] / n);
+  }
   return GNK_OK;
 }
 
@@ -118,7 +159,7 @@ using namespace gnk;
 extern "C" int64_t gnk_gemm_rs_flag_words(int64_t M, int64_t N, int world) {
   RsPlan p;
   if (make_plan(M, N, world, &p) != GNK_OK) return -1;
-  return p.units + 2;
+  return 2 * p.units + 2;  // arrivals and finished-chunk counts per unit, CTA ticket, exit barrier
 }
 
 // Host-side restatement of the device tile order, for tests: sequence index i -> the 128 x BN
@@ -143,9 +184,10 @@ extern "C" int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, i
   return total;
 }
 
-extern "C" int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
-                                int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
-                                int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream) {
+namespace {
+int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging, const void* multicast,
+                 int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N, int64_t K_local, int rank,
+                 int world, uint32_t timeout_ms, gnk_stream_t stream) {
   if (!x || !w || !output || M <= 0 || N <= 0 || K_local <= 0) return GNK_ERR_BAD_ARG;
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return GNK_ERR_BAD_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(output)) return GNK_ERR_BAD_ALIGN;
@@ -177,8 +219,26 @@ extern "C" int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64
     g.rs.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
   }
   g.dbg = rs_debug_bits();
+  g.rs.mc_partial = static_cast<const __nv_bfloat16*>(multicast);
   g.rs.out = static_cast<__nv_bfloat16*>(output);
   g.rs.ldo = ldo;
   if (p.cg == 2) return launch_rs<256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
   return launch_rs<128, 1>(x, ldx, w, ldw, g, M, N, K_local, st);
+}
+}  // namespace
+
+extern "C" int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
+                                int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
+                                int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream) {
+  return gemm_rs_impl(x, ldx, w, ldw, staging, nullptr, flags, output, ldo, M, N, K_local, rank, world, timeout_ms,
+                      stream);
+}
+
+extern "C" int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* partial,
+                                     const void* partial_multicast, int32_t* const* flags, void* output, int64_t ldo,
+                                     int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
+                                     gnk_stream_t stream) {
+  if (world > 1 && (!partial_multicast || !aligned16(partial_multicast))) return GNK_ERR_BAD_ARG;
+  return gemm_rs_impl(x, ldx, w, ldw, partial, partial_multicast, flags, output, ldo, M, N, K_local, rank, world,
+                      timeout_ms, stream);
 }

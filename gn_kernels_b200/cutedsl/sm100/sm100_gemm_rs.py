@@ -33,12 +33,17 @@ def gemm_rs(
     *,
     BN: int | None = None,
     timeout_ms: int = 0,
+    multicast: bool | None = None,
 ) -> torch.Tensor:
     """output[M/W, N] = sum over ranks of bf16(x_r @ w_r^T)[this rank's rows], fp32 summation.
 
-    x [M, K/W], w [N, K/W] bf16 (this rank's K shard).  `partial` is used as staging: every rank
-    stores its bf16 tiles into the owner's buffer over NVLink, the owner reduces from its own
-    memory.  Device-side waits are bounded by `timeout_ms` (0 = 20 s); a wait that runs out is
+    x [M, K/W], w [N, K/W] bf16 (this rank's K shard).  Two data paths share the flag protocol:
+    with an NVLink multicast address for `partial` (`partial_handle.multicast_ptr`, NVSwitch
+    systems) every rank keeps its bf16 tiles in its own `partial` and the owner reads them with
+    multimem.ld_reduce, as upstream does; without one, every rank stores its tiles into the owner's
+    buffer over NVLink and the owner reduces from its own memory.  `multicast` = None picks the
+    first when the handle offers an address, True requires it, False forces the second.
+    Device-side waits are bounded by `timeout_ms` (0 = 20 s); a wait that runs out is
     reported by `gn_kernels_b200._lib.raise_on_device_error()`.  BN is accepted for upstream
     compatibility; the tile shape is chosen from the problem shape."""
     assert dist.is_initialized()
@@ -58,6 +63,26 @@ def gemm_rs(
     else:
         sp = fp = None
     stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    mc = 0
+    if world > 1 and multicast is not False:
+        try:
+            mc = int(getattr(partial_handle, "multicast_ptr", 0) or 0)
+        except Exception:
+            mc = 0
+        if mc == 0 and multicast:
+            raise RuntimeError("gemm_rs: multicast=True but the symmetric-memory handle has no multicast address")
+    if mc:
+        mc += partial.storage_offset() * partial.element_size()
+        with torch.cuda.device(x.device):
+            check(
+                lib().gnk_gemm_rs_bf16_pull(
+                    ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(w.data_ptr()), w.stride(0), sp,
+                    ctypes.c_void_p(mc), fp, ctypes.c_void_p(output.data_ptr()), output.stride(0), M, N, K, rank, world,
+                    timeout_ms, stream,
+                ),
+                "gnk_gemm_rs_bf16_pull",
+            )
+        return output
     with torch.cuda.device(x.device):
         check(
             lib().gnk_gemm_rs_bf16(

@@ -205,6 +205,17 @@ int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, voi
                      int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
                      int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream);
 
+/* Same operation for buffers that also have an NVLink multicast address (NVSwitch systems):
+ * partial[r] are the ranks' [M, N] bf16 buffers (only partial[rank] is written, by this rank),
+ * partial_multicast the multicast address of the same allocation.  A finished tile stays in the
+ * rank's own buffer; the owner reads every 16-byte piece once with multimem.ld_reduce (fp32 adds in
+ * the switch), as upstream does (sm100_gemm_rs.py:27-60, 283-327).  flags as above.
+ * Replaces: gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496 `gemm_rs`. */
+int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* partial,
+                          const void* partial_multicast, int32_t* const* flags, void* output, int64_t ldo,
+                          int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
+                          gnk_stream_t stream);
+
 /* ------------------------------------------------------------------ test hooks ---- */
 /* Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, -1: automatic),
  * cap the persistent grid (0 = no cap), record per-stage clock stamps of CTAs 0 and 1 into a device

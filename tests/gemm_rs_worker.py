@@ -19,20 +19,26 @@ sys.path.insert(0, ROOT)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--k-total", type=int, default=28672, help="bench: K summed over ranks")
+    ap.add_argument("--symm-backend", default="", help="torch symmetric-memory backend (empty = torch's default)")
+    ap.add_argument("--multicast", type=int, default=-1, help="-1 automatic, 0 push over peer stores, 1 pull through the multicast address")
     args = ap.parse_args()
     from gn_kernels_b200 import _lib
-    from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import flag_words, gemm_rs
+    from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import flag_words
+    from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import gemm_rs as _gemm_rs
     from oracle import gemm_rs as ors
     from oracle.mm import max_rel_err
 
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    try:
-        symm_mem.set_backend("NCCL")
-    except Exception:
-        pass
+    if args.symm_backend:  # torch's default backend offers a multicast address on NVSwitch systems
+        symm_mem.set_backend(args.symm_backend)
     rank, W = dist.get_rank(), dist.get_world_size()
+    mcast = None if args.multicast < 0 else bool(args.multicast)
+
+    def gemm_rs(*a, **k):  # every call below goes through the chosen data path
+        return _gemm_rs(*a, multicast=mcast, **k)
 
     def alloc(M, N):
         partial = symm_mem.empty(M, N, dtype=torch.bfloat16, device=dev)
@@ -41,6 +47,10 @@ def main():
         flags.zero_()
         fh = symm_mem.rendezvous(flags, dist.group.WORLD)
         dist.barrier()
+        if rank == 0:
+            has_mc = bool(getattr(ph, "multicast_ptr", 0))
+            path = "pull (multimem.ld_reduce)" if (has_mc and mcast is not False) else "push (peer stores)"
+            print(f"gemm_rs data path: {path}; multicast address available: {has_mc}", flush=True)
         return partial, ph, flags, fh
 
     failures = 0
@@ -76,7 +86,7 @@ def main():
 
     if args.bench:
         M = N = 8192
-        Kt = 28672
+        Kt = args.k_total
         Kl = Kt // W
         g = torch.Generator().manual_seed(1234 + rank)
         x = (torch.randn(M, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)

@@ -37,7 +37,7 @@ def test_tile_order_covers_everything_once_and_spreads_owners(M, N, W):
         for i, (owner, tm, tn, unit, nunits) in enumerate(rows):
             assert (tm, tn) not in seen
             seen.add((tm, tn))
-            assert 0 <= owner < W and 0 <= unit and unit + (nunits - 1) * (N // (256 if nunits == 2 else 128)) < words - 2
+            assert 0 <= owner < W and 0 <= unit and unit + (nunits - 1) * (N // (256 if nunits == 2 else 128)) < (words - 2) // 2
             # at every step the ranks target pairwise different owners
             assert owner == (rank + 1 + i) % W
             for k in range(nunits):
@@ -46,7 +46,8 @@ def test_tile_order_covers_everything_once_and_spreads_owners(M, N, W):
         assert len(seen) == total
     # every owned unit is signalled exactly once by every rank
     assert set(signals.values()) == {W}
-    assert len(signals) == W * (words - 2)
+    # flag words: one arrival word and one finished-chunk word per unit, plus ticket and exit barrier
+    assert len(signals) == W * ((words - 2) // 2)
 
 
 def test_bad_shapes_rejected():

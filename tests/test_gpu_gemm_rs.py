@@ -12,12 +12,15 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_gemm_rs_all_ranks():
+@pytest.mark.parametrize("multicast", [0, -1], ids=["push", "pull-if-multicast"])
+def test_gemm_rs_all_ranks(multicast):
+    """Both data paths against the oracle: peer stores into the owner's slots, and (where the
+    symmetric-memory handle offers a multicast address) multimem.ld_reduce pulls."""
     world = min(torch.cuda.device_count(), 8)
     world = 1 << (world.bit_length() - 1)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", "29531", os.path.join(ROOT, "tests", "gemm_rs_worker.py")]
+           "--master-port", "29531", os.path.join(ROOT, "tests", "gemm_rs_worker.py"), "--multicast", str(multicast)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0 and "GEMM_RS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
