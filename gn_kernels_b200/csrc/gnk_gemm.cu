@@ -47,7 +47,9 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   const CUtensorMapDataType dt = KIND == MmaKind::F16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const uint64_t k_elems_tm = KIND == MmaKind::F16 ? K : k_bytes;  // tensor-map inner extent in its own elements
   const uint32_t box_inner = KIND == MmaKind::F16 ? 64 : 128;
-  int rc = make_tmap_2d(&tm_a, dt, A, M, k_elems_tm, lda_b, 128, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
+  g.a_rows = M < 128 ? static_cast<int>((M + 7) / 8 * 8) : 128;
+  g.stages = C::stages_for(g.a_rows);
+  int rc = make_tmap_2d(&tm_a, dt, A, M, k_elems_tm, lda_b, g.a_rows, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
   rc = make_tmap_2d(&tm_b, dt, Bt, N, k_elems_tm, ldb_b, BN / CG, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;

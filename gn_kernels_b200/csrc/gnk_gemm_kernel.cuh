@@ -31,6 +31,8 @@ struct GemmArgs {
   float alpha;
   int vec_ok;  // C rows 16-byte aligned: vector stores allowed
   long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
+  int a_rows;        // rows of A one stage load brings in (the tensor map's box; 128 unless M < 128)
+  int stages;        // pipeline depth (the launcher's choice: fewer A rows per stage leave room for more stages)
   int dbg;           // debug bits (timing experiments only, wrong results): 1 skip scale-factor copies, 2 reduce-scatter reducers only wait, 4 reduce-scatter stores stay local
   // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
   // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
@@ -95,6 +97,13 @@ struct Cfg {
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = kStages * kStageBytes + 2048 + kEpiBytes;
+  static constexpr int kMaxStages = 24;  // barrier words stay well inside the 2 KB reserve
+  // pipeline depth when a stage holds only a_rows rows of A
+  static int stages_for(int a_rows) {
+    if (a_rows >= 128) return kStages;
+    const int n = (kStages * kStageBytes) / (kStageBytes - (128 - a_rows) * 128);
+    return n > kMaxStages ? kMaxStages : n;
+  }
   // TMEM columns
   static constexpr int kSfaCols = KI::kSfPerStage;                      // 4 bytes per column, 128 rows -> 4 columns per 4 scales
   static constexpr int kSfbCols = KI::kSfPerStage * kSfbGroups;
@@ -357,7 +366,12 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
                 const __grid_constant__ EpiMaps<EPI> epi_maps, const GemmArgs g) {
   using C = Cfg<KIND, BN, CG, EPI, STG>;
   constexpr bool kBS = C::KI::kBlockScaled;
-  constexpr int S = C::kStages;
+  // A problem with fewer than 128 rows loads and holds only those rows of A per stage (rows beyond
+  // them read stale shared memory and only feed accumulator rows that are never stored).  A skinny
+  // GEMM is the DRAM stream of B, and its rate is set by the bytes in flight: the space saved on A
+  // goes into more pipeline stages.
+  const int S = g.stages;
+  const uint32_t a_bytes = static_cast<uint32_t>(g.a_rows) * 128u;
   constexpr int kInner = KIND == MmaKind::F16 ? 64 : 128;  // tensor-map elements per 128-byte K stage
 
   extern __shared__ uint8_t smem_raw[];
@@ -366,9 +380,9 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   // the bulk-store staging (read by TMA in the 128-byte swizzle, hence 1024-byte aligned) comes first
   constexpr bool kEpiFirst = C::kBulkC || (EPI == EPI_RS && C::kStaged);
   const uint32_t ab_base = smem_base + (kEpiFirst ? C::kEpiBytes : 0);
-  auto stage_a = [&](int s) { return ab_base + s * (C::kABytes + C::kBBytes); };
-  auto stage_b = [&](int s) { return stage_a(s) + C::kABytes; };
-  const uint32_t sf_base = ab_base + S * (C::kABytes + C::kBBytes);
+  auto stage_a = [&](int s) { return ab_base + s * (a_bytes + C::kBBytes); };
+  auto stage_b = [&](int s) { return stage_a(s) + a_bytes; };
+  const uint32_t sf_base = ab_base + S * (a_bytes + C::kBBytes);
   auto stage_sfa = [&](int s) { return sf_base + s * (C::kSfaBytes + C::kSfbBytes); };
   auto stage_sfb = [&](int s) { return stage_sfa(s) + C::kSfaBytes; };
   const uint32_t bar_base = sf_base + S * (C::kSfaBytes + C::kSfbBytes);
@@ -433,6 +447,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     const bool leader = elect_one();
     uint32_t stage = 0, parity = 1;
     bool ok = true;
+    const uint32_t stage_tx = C::kStageBytes - (128 - g.a_rows) * 128;
     // both CTAs of a pair count their bytes on CTA 0's barrier
     const uint32_t full0 = CG == 2 ? map_to_cta(bar_full(0), 0) : bar_full(0);
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
@@ -450,7 +465,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         const uint32_t sa = stage_a(stage), sb = stage_b(stage);
         if (leader) {
           if constexpr (CG == 2) {
-            mbar_expect_tx_cluster(full, C::kStageBytes);
+            mbar_expect_tx_cluster(full, stage_tx);
             tma_load_2d_pair(sa, &tm_a, full, k * kInner, a_row);
             tma_load_2d_pair(sb, &tm_b, full, k * kInner, b_row);
             if constexpr (kBS) {
@@ -458,7 +473,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
               tma_load_2d_pair(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), sfb_row);
             }
           } else {
-            mbar_expect_tx(full, C::kStageBytes);
+            mbar_expect_tx(full, stage_tx);
             tma_load_2d(sa, &tm_a, full, k * kInner, a_row);
             tma_load_2d(sb, &tm_b, full, k * kInner, b_row);
             if constexpr (kBS) {

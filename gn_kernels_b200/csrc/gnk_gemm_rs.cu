@@ -75,6 +75,8 @@ int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g
   rc = make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, w, N, K, ldw * 2, BN / CG, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
   g.k_iters = static_cast<int>((K * 2 + 127) / 128);
+  g.a_rows = 128;
+  g.stages = C::kStages;
   auto kern = gemm_kernel<MmaKind::F16, BN, CG, EPI_RS>;
   static int resident[64];
   int dev = 0;
