@@ -106,7 +106,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.fh.close()
-        clocks, reasons, mx = [], set(), None
+        rows = []
         with open(self.path) as fh:
             for line in fh:
                 f = [x.strip() for x in line.split(",")]
@@ -117,16 +117,23 @@ class ClockSampler:
                     clk, cmax = float(f[1]), float(f[2])
                 except ValueError:
                     continue
-                if not (t_begin <= ts <= t_end):
-                    continue
-                clocks.append(clk)
-                mx = cmax
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+                rows.append((ts, clk, cmax, f[5:9]))
         os.unlink(self.path)
-        if clocks:
-            out.update(sm_mhz=float(np.median(clocks)), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(clocks))
+        inside = [r for r in rows if t_begin <= r[0] <= t_end]
+        if not inside and rows:
+            # a timed region shorter than the sampling period: the sample nearest to it (the untimed
+            # lead-in keeps the GPU under the same load right before), with its distance stated
+            near = min(rows, key=lambda r: min(abs(r[0] - t_begin), abs(r[0] - t_end)))
+            inside = [near]
+            out["nearest_sample_ms_from_timed_region"] = round(1e3 * min(abs(near[0] - t_begin), abs(near[0] - t_end)), 1)
+        reasons = set()
+        for r in inside:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if inside:
+            out.update(sm_mhz=float(np.median([r[1] for r in inside])), sm_max_mhz=inside[-1][2], reasons=sorted(reasons),
+                       samples=len(inside))
         return out
 
 
