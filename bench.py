@@ -15,8 +15,9 @@ Other workloads (--workload): NVFP4 / INT8 / BF16 GEMMs, skinny MXFP8 decode sha
 NVFP4 quantizer (GB/s) and the FP8-QK causal GQA attention of the reference's benchmark
 configuration.  With --gpus N > 1 (under torchrun) every rank runs the same workload on
 its own GPU: these ops do not shard ("replicas only"), scaling is weak and `value` is the
-sum over ranks.  The K-sharded GEMM + reduce-scatter has its own driver
-(tests/gemm_rs_worker.py --bench) because it needs symmetric memory across ranks.
+sum over ranks.  The one op that shards is the K-sharded BF16 GEMM + reduce-scatter
+(--workload bf16_gemm_rs under torchrun): the global problem is fixed, every rank holds
+K/N of it, symmetric memory carries the exchange, and scaling is "strong".
 
 --impl reference times the CPU restatement of the upstream torch reference path
 (oracle/) on the host cores with every thread torch can use, same workload and metric,
@@ -58,6 +59,7 @@ WORKLOADS = {
     "mxfp8_gemm_m16": ("gemm", "MXFP8 GEMM TFLOPS at M=16, N=K=8192", (16, 8192, 8192)),
     "mxfp8_gemm_m64": ("gemm", "MXFP8 GEMM TFLOPS at M=64, N=K=8192", (64, 8192, 8192)),
     "mxfp8_gemm_m128": ("gemm", "MXFP8 GEMM TFLOPS at M=128, N=K=8192", (128, 8192, 8192)),
+    "bf16_gemm_rs": ("rs", "BF16 GEMM + reduce-scatter TFLOPS at M=N=8192, K=28672 sharded over the ranks", (8192, 8192, 28672)),
     "nvfp4_quant_8192": ("quant", "NVFP4 quantizer GB/s at 8192x8192 bf16", (8192, 8192)),
     "attn_fp8_causal": ("attn", "FP8-QK causal GQA attention TFLOPS (B=4, Hq=32, Hkv=8, L=4096, D=128)", (4, 4096, 32, 8, 128)),
 }
@@ -204,6 +206,46 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
             algo_bytes = 2 * (M + N) * K + 2 * M * N
         w.update(work=2.0 * M * N * K, unit="TOP/s" if kind == "int8" else "TFLOP/s", scale=1e12, ins=ins, outs=[C], api=api, step=step,
                  algo_bytes=algo_bytes, bound="hbm" if M <= 128 else "tensor", config={"M": M, "N": N, "K": K})
+    elif family == "rs":
+        # K is sharded over the ranks (strong scaling: the global problem is fixed); every rank ends
+        # with its M/world rows of the reduced product.  One rank: the plain GEMM it degenerates to.
+        import torch.distributed as dist
+
+        M, N, Kt = shape
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        Kl = Kt // world
+        g = torch.Generator(device="cpu").manual_seed(SEED_MM + rank)
+        x = (torch.randn(M, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)
+        wt = (torch.randn(N, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)
+        out = torch.empty(M // world, N, dtype=torch.bfloat16, device=dev)
+        path = "single GPU: plain GEMM"
+        if world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import flag_words, gemm_rs
+
+            partial = symm_mem.empty(M, N, dtype=torch.bfloat16, device=dev)
+            ph = symm_mem.rendezvous(partial, dist.group.WORLD)
+            flags = symm_mem.empty(flag_words(M, N, world), dtype=torch.int32, device=dev)
+            flags.zero_()
+            fh = symm_mem.rendezvous(flags, dist.group.WORLD)
+            dist.barrier()
+            path = "pull through the NVLink multicast address (multimem.ld_reduce)" if getattr(ph, "multicast_ptr", 0) else "push by peer stores"
+
+            def step():
+                gemm_rs(x, wt, partial, ph, out, flags, fh)
+                return 0
+
+            api = lambda a, b: gemm_rs(a, b, partial, ph, out, flags, fh)  # noqa: E731
+            w["extra_resident"] = partial.numel() * 2
+        else:
+            step = lambda: L.gnk_mm_bf16(P(x), Kl, P(wt), Kl, P(out), N, M, N, Kl, stream())  # noqa: E731
+            api = lambda a, b: gk.cutedsl.sm100.sm100_mm_bf16.mm(a, b.T)  # noqa: E731
+        w.update(work=2.0 * M * N * Kt / world, unit="TFLOP/s", scale=1e12, ins=[x, wt], outs=[out], api=api, step=step, kind="bf16",
+                 algo_bytes=2 * (M + N) * Kl + 2 * M * N, bound="tensor", scaling="strong",
+                 config={"M": M, "N": N, "K_total": Kt, "K_per_rank": Kl, "data_path": path,
+                         "nvlink_bytes_per_rank": (world - 1) * M * N * 2 // world})
     elif family == "quant":
         M, K = shape
         g = torch.Generator(device="cpu").manual_seed(SEED_MM)
@@ -242,7 +284,7 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
         out = w["api"](*dev_in)
         out_host.copy_(out.view(out_host.dtype) if out.dtype != out_host.dtype else out, non_blocking=True)
 
-    w.update(host_step=host_step, h2d=_nbytes(pinned), d2h=_nbytes([out_host]), resident_bytes=_nbytes(w["ins"]) + _nbytes(w["outs"]))
+    w.update(host_step=host_step, h2d=_nbytes(pinned), d2h=_nbytes([out_host]), resident_bytes=_nbytes(w["ins"]) + _nbytes(w["outs"]) + w.get("extra_resident", 0))
     return w
 
 
@@ -256,7 +298,7 @@ def build_cpu_workload(name: str, rows: int):
 
     family, metric, shape = WORKLOADS[name]
     kind = name.split("_")[0]
-    if family == "gemm":
+    if family in ("gemm", "rs"):  # the reduce-scatter's CPU arm is the global product on the row sample
         M, N, K = shape
         rows = min(rows, M)
         g = torch.Generator(device="cpu").manual_seed(SEED_MM)
@@ -323,7 +365,7 @@ def run_reference(args, rank: int):
     cores = torch.get_num_threads()
     line = {
         "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
+        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if family == "rs" else "weak", "vs_baseline": None, "dtype": kind,
         "data": "synthetic", "config": {"workload": args.workload, "shape": list(shape), "sample": sample},
         "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -429,13 +471,15 @@ def run_gpu(args, rank: int, local_rank: int, world: int):
                         "peak_source": f"copy bandwidth {peaks['hbm_gbs']} GB/s ({peaks['src']})", "kernel_ms": avg_ms}
         cstep, cwork, sample = build_cpu_workload(args.workload, args.cpu_rows)
         ctot = time_cpu(cstep, 2, 1)
-        cfg = {"workload": args.workload, **w["config"], "parallelism": "replicas only" if world > 1 else "single GPU",
+        cfg = {"workload": args.workload, **w["config"],
+               "parallelism": (f"K sharded over {world} ranks, reduce-scatter along M" if w.get("scaling") == "strong" and world > 1
+                               else "replicas only" if world > 1 else "single GPU"),
                "l2": (f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB > 126 MB L2 (no flush needed)" if flush_buf is None
                       else f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB could stay in L2: 252 MiB written between steps, steps timed one by one"),
                "lead_in_steps": args.lead_in}
         line = {
             "metric": w["metric"], "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warm,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": w.get("scaling", "weak"), "vs_baseline": None,
             "dtype": kind, "data": "synthetic", "config": cfg, "roofline": roofline,
             "cpu_baseline": {"value": cwork * 2 / ctot / scale, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample + ", 2 timed passes"},
             "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"], "steps": e2e_steps},
