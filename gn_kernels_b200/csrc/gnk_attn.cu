@@ -44,6 +44,7 @@ struct AttnArgs {
   const float* scale_k;
   __nv_bfloat16* o;
   int64_t o_sb, o_sl, o_sh;
+  long long* trace;  // debug: clock64 stamps of CTA 0, softmax warps 0 and 4, 8 per key tile (null = off)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -234,6 +235,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     float m_used = -1e38f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
+      long long* tr = (a.trace && blockIdx.x == 0 && (warp & 3) == 0 && lane == 0 && j < 32) ? a.trace + (t * 32 + j) * 8 : nullptr;
+      if (tr) tr[0] = clock64();
       // stage the tile's key scales (one per thread of this group), 0 beyond the sequence
       {
         const int col = j * kBN + r;
@@ -244,6 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!mbar_wait(bar_sfull(t), j & 1, (0x13u << 24) | (1u << 16) | j)) { ok = false; break; }
       tc_fence_after();
+      if (tr) tr[1] = clock64();
       const int col0 = j * kBN;
       const bool need_mask = col0 + kBN - 1 > min(row0 + shift, a.Lk - 1) && (a.causal || col0 + kBN > a.Lk);
       // ---- pass 1: row maximum of x = S * scale_k[col]; the positive row factor qs is applied once at the end ----
@@ -270,6 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       };
       if (need_mask) pass1(std::true_type{}); else pass1(std::false_type{});
+      if (tr) tr[2] = clock64();
       // qs >= 0 (absmax scales), so max(qs * x) = qs * max(x); a fully masked row keeps the old maximum
       const float mt = fmaxf(m_used, xmax == -INFINITY ? -INFINITY : qs * xmax);
       // lazy rescale, decided per warp so the TMEM traffic stays warp-collective
@@ -296,6 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       // ---- pass 2: P = exp2(qs * x - max), row sum, bf16 P into shared memory ----
+      if (tr) tr[3] = clock64();
       float rs = 0.f;
       const float neg_m = -m_used;
       auto pass2 = [&](auto masked) {
@@ -331,11 +337,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       };
       if (need_mask) pass2(std::true_type{}); else pass2(std::false_type{});
+      if (tr) tr[4] = clock64();
       l += rs;
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pready(t));
+      if (tr) tr[5] = clock64();
     }
 
     // epilogue: O / l -> bf16
@@ -378,6 +386,15 @@ GNK_DEFINE_STATUS_READER(attn_status_reader)
 
 using namespace gnk;
 
+namespace {
+long long* g_attn_trace = nullptr;
+}
+// Test hook: device buffer of 2 * 32 * 8 int64 receiving clock64 stamps (see AttnArgs::trace); NULL = off.
+extern "C" int gnk_debug_attn_trace(void* device_buffer) {
+  g_attn_trace = static_cast<long long*>(device_buffer);
+  return GNK_OK;
+}
+
 extern "C" int gnk_attn_fwd(const void* q, const void* k, const void* v, void* o, const float* scale_q,
                             const float* scale_k, int qk_kind, int64_t B, int64_t Lq, int64_t Lk, int64_t Hq,
                             int64_t Hkv, int64_t D, const int64_t* q_strides, const int64_t* k_strides,
@@ -410,6 +427,7 @@ extern "C" int gnk_attn_fwd(const void* q, const void* k, const void* v, void* o
   if ((rc = make(&tm_v, v, Lk, Hkv, v_strides, 2, 64, kBN, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)) != GNK_OK) return rc;
 
   AttnArgs a{};
+  a.trace = g_attn_trace;
   a.Lq = static_cast<int>(Lq);
   a.Lk = static_cast<int>(Lk);
   a.Hq = static_cast<int>(Hq);

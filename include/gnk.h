@@ -225,6 +225,7 @@ int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default (staged), 0 di
 int gnk_debug_max_clusters(int n);
 int gnk_debug_flags(int bits); /* timing experiments only: bit 0 skips scale-factor copies (wrong results) */
 int gnk_debug_trace(void* device_buffer);
+int gnk_debug_attn_trace(void* device_buffer); /* attention: clock stamps of CTA 0, 2 tiles x 32 key tiles x 8 int64 (NULL = off) */
 
 #ifdef __cplusplus
 }
