@@ -358,6 +358,10 @@ def run_reference(args, rank: int):
         return
     family, metric, shape = WORKLOADS[args.workload]
     kind = args.workload.split("_")[0]
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # a multi-rank launcher pins every rank to one OpenMP thread; this arm is a host benchmark on
+        # rank 0 alone, so it takes every core it can get back
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     step, work, sample = build_cpu_workload(args.workload, args.cpu_rows)
     total = time_cpu(step, args.steps, max(1, min(args.warmup, 1)))
     unit, scale = ("GB/s", 1e9) if family == "quant" else (("TOP/s" if kind == "int8" else "TFLOP/s"), 1e12)
@@ -469,8 +473,12 @@ def run_gpu(args, rank: int, local_rank: int, world: int):
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_bytes": w["algo_bytes"],
                         "peak_source": f"copy bandwidth {peaks['hbm_gbs']} GB/s ({peaks['src']})", "kernel_ms": avg_ms}
-        cstep, cwork, sample = build_cpu_workload(args.workload, args.cpu_rows)
-        ctot = time_cpu(cstep, 2, 1)
+        cpu_baseline = None  # timed at N = 1 only (the launcher pins ranks to one host thread each)
+        if world == 1:
+            cstep, cwork, sample = build_cpu_workload(args.workload, args.cpu_rows)
+            ctot = time_cpu(cstep, 2, 1)
+            cpu_baseline = {"value": cwork * 2 / ctot / scale, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+                            "sample": sample + ", 2 timed passes"}
         cfg = {"workload": args.workload, **w["config"],
                "parallelism": (f"K sharded over {world} ranks, reduce-scatter along M" if w.get("scaling") == "strong" and world > 1
                                else "replicas only" if world > 1 else "single GPU"),
@@ -481,7 +489,7 @@ def run_gpu(args, rank: int, local_rank: int, world: int):
             "metric": w["metric"], "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": w.get("scaling", "weak"), "vs_baseline": None,
             "dtype": kind, "data": "synthetic", "config": cfg, "roofline": roofline,
-            "cpu_baseline": {"value": cwork * 2 / ctot / scale, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample + ", 2 timed passes"},
+            "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"], "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks,
         }
