@@ -65,7 +65,7 @@ WORKLOADS = {
 }
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures
 # under profiles/; None where no capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"mxfp8_gemm_8192": 356.7e6 + 117.0e6}
+NCU_TRAFFIC_BYTES = {"mxfp8_gemm_8192": 356.7e6 + 117.0e6, "attn_fp8_causal": 120.2e6 + 88.1e6, "nvfp4_quant_8192": 134.2e6 + 20.4e6}
 
 
 def load_peaks():
