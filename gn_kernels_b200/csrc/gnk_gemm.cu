@@ -3,7 +3,10 @@
 // bias, raw int32).
 //
 // One persistent, warp-specialised kernel template:
-//   warps 0-3  epilogue: TMEM -> registers (tcgen05.ld, lane = row) -> scale/cast -> global
+//   warps 0-3  epilogue: TMEM -> registers (tcgen05.ld, lane = row) -> scale/cast -> global.  The
+//              256 x 256 pair tile stages bf16 output in two swizzled 4 KB buffers per warp and
+//              writes it with bulk tensor stores (cp.async.bulk.tensor shared -> global); the
+//              other tiles store from registers
 //   warp  4    producer: one lane issues the TMA loads of a K stage (A, B, and for the
 //              block-scaled kinds the 512-byte scale-factor atoms) onto a full barrier
 //   warp  5    MMA: one lane copies scale atoms smem -> TMEM (tcgen05.cp) and issues four

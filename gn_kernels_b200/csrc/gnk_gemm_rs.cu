@@ -1,16 +1,18 @@
 // BF16 GEMM fused with a reduce-scatter over NVLink peer memory (K sharded across ranks).
 //
-// Every rank computes its [M, N] partial tile by tile with the tcgen05 GEMM kernel; the epilogue
-// rounds a tile to bf16 and stores it straight into the staging slot (indexed by the sending
-// rank) of the rank that owns those rows, then bumps that owner's flag for the tile with a
-// system-scope release.  Four extra warps per CTA on the owner wait (bounded) until a tile's
-// flag shows all ranks, add the slots in fp32 from the owner's own HBM and write the bf16
-// output rows.  The kernel ends with a cross-rank exit barrier so that the next call cannot
-// overwrite staging that a slower rank is still reducing.  The 256-wide pair tile leaves through
-// bulk tensor STORES (shared memory -> the owner's slot, 64 x 32 boxes) whose completion the issuing
-// lane awaits before the flag is signalled; the 128-wide fallback uses plain peer stores.  Only
-// stores and atomics cross NVLink: every load is local, no TMA load names peer memory and none
-// uses cluster multicast.
+// Every rank computes its [M, N] partial tile by tile with the tcgen05 GEMM kernel; each epilogue
+// warp rounds its 32 x 256 piece to bf16, stages it in shared memory and hands it to bulk tensor
+// stores.  Push variant: the stores go straight into the staging slot (indexed by the sending
+// rank) of the rank that owns those rows.  The warp signals the owner's flag word for the
+// 128 x 256 unit (system-scope release, one signal per warp) once the stores have completed;
+// that wait is deferred to the start of the warp's next tile, where it costs nothing.  Four extra
+// warps per CTA on the owner take work items in the order the tiles are produced, wait (bounded)
+// until a unit's flag shows all warps of all ranks, add the slots in fp32 from the owner's own
+// HBM and write the bf16 output rows; the last item of a unit clears its words.  The kernel ends
+// with a cross-rank exit barrier so that the next call cannot overwrite staging that a slower
+// rank is still reducing.  The 128-wide fallback tile uses plain peer stores.  Only stores and
+// atomics cross NVLink in this variant: every load is local, no TMA load names peer memory and
+// none uses cluster multicast.
 //
 // Pull variant (gnk_gemm_rs_bf16_pull, for buffers that also have an NVLink multicast address):
 // a finished tile stays in the rank's OWN [M, N] partial; only the flag update crosses NVLink.  The
