@@ -363,7 +363,15 @@ def run_reference(args, rank: int):
         # rank 0 alone, so it takes every core it can get back
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     step, work, sample = build_cpu_workload(args.workload, args.cpu_rows)
-    total = time_cpu(step, args.steps, max(1, min(args.warmup, 1)))
+    # Keep the whole run within a few minutes whatever --steps says: one probe step; if K steps would
+    # take longer than about five minutes, fewer steps are executed and the line says how many (the
+    # per-step cost is dominated by dequantising the full B operand, so a smaller row sample would
+    # not shorten it).
+    t_probe = time_cpu(step, 1, 0)
+    executed = args.steps
+    if t_probe * args.steps > 300.0:
+        executed = max(2, int(300.0 / t_probe))
+    total = time_cpu(step, executed, 0) * args.steps / executed
     unit, scale = ("GB/s", 1e9) if family == "quant" else (("TOP/s" if kind == "int8" else "TFLOP/s"), 1e12)
     val = work * args.steps / total / scale
     cores = torch.get_num_threads()
@@ -373,7 +381,7 @@ def run_reference(args, rank: int):
         "data": "synthetic", "config": {"workload": args.workload, "shape": list(shape), "sample": sample},
         "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0, "host_cpus": os.cpu_count(),
+        "gpu_launches": 0, "host_cpus": os.cpu_count(), "steps_executed": executed,
     }
     print(json.dumps(line), flush=True)
 
