@@ -60,3 +60,35 @@ def test_cpu_tensors_raise():
         gk.quantize_nvfp4(torch.randn(16, 64).bfloat16())
     with pytest.raises(RuntimeError):
         gk.triton_mm(torch.zeros(16, 16, dtype=torch.int8), torch.zeros(16, 16, dtype=torch.int8))
+
+
+def declared_prototypes():
+    """name -> number of parameters, parsed from include/gnk.h (comments stripped)."""
+    text = open(os.path.join(ROOT, "include", "gnk.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = {}
+    for name, params in re.findall(r"\b(gnk_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S):
+        params = params.strip()
+        protos[name] = 0 if params in ("", "void") else params.count(",") + 1
+    return protos
+
+
+def test_ctypes_signatures_have_the_header_parameter_counts():
+    from gn_kernels_b200 import _lib
+
+    protos = declared_prototypes()
+    assert len(protos) >= 20
+    for name, n in protos.items():
+        restype, argtypes = _lib._SIGNATURES[name]
+        assert len(argtypes) == n, f"{name}: gnk.h declares {n} parameters, the ctypes table has {len(argtypes)}"
+
+
+def test_gemm_rs_pull_entry_refuses_a_missing_multicast_address():
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.c_void_p(ctypes.addressof(buf) // 16 * 16 + 16)
+    arr = (ctypes.c_void_p * 2)(p, p)
+    rc = L.gnk_gemm_rs_bf16_pull(p, 64, p, 64, arr, ctypes.c_void_p(0), arr, p, 256, 512, 256, 64, 0, 2, 0, ctypes.c_void_p(0))
+    assert rc == _lib.ERR_BAD_ARG
