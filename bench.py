@@ -1,27 +1,30 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized-matmul / quantizer / attention hot path on B200.
+"""Benchmark of the quantized-matmul / quantizer / attention / GEMM + reduce-scatter hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference] [--kernel-only]
 
-Default workload: MXFP8 GEMM, M = N = K = 8192 (E4M3 values, one E8M0 scale per 32 K
-elements, fp32 accumulate, bf16 output), synthetic N(0,1) data quantised on the GPU
-before the timed region.  One "step" = one pass of the workload's kernel over resident
-operands.  The JSON line carries: `value` (device-timed, whole job), `e2e` (the same call
-through the public Python API from pinned HOST buffers, copies inside the timed region),
-`roofline` for the kernel, `cpu_baseline` (the oracle on the host cores, bounded sample),
-and the SM clocks sampled while the GPU was in the loaded state the timed steps ran in.
+Default workload at EVERY N: the K-sharded BF16 GEMM + reduce-scatter, C[8192, 8192] =
+A[8192, 28672] * B[28672, 8192] with K split evenly over the N ranks (strong scaling: the global
+problem is fixed), every rank ending with its 8192/N rows of the reduced product.  N = 1 is the
+plain GEMM the op degenerates to.  One "step" = one call of the op on resident operands.  Under
+torchrun (N > 1) symmetric memory carries the exchange and every rank runs the same number of steps.
 
-Other workloads (--workload): NVFP4 / INT8 / BF16 GEMMs, skinny MXFP8 decode shapes, the
-NVFP4 quantizer (GB/s) and the FP8-QK causal GQA attention of the reference's benchmark
-configuration.  With --gpus N > 1 (under torchrun) every rank runs the same workload on
-its own GPU: these ops do not shard ("replicas only"), scaling is weak and `value` is the
-sum over ranks.  The one op that shards is the K-sharded BF16 GEMM + reduce-scatter
-(--workload bf16_gemm_rs under torchrun): the global problem is fixed, every rank holds
-K/N of it, symmetric memory carries the exchange, and scaling is "strong".
+The JSON line carries: `value` (device-timed, whole job), `e2e` (the public Python API from pinned
+HOST buffers, copies inside the timed region, copies of neighbouring steps overlapped with the
+kernel), `roofline` (tensor and NVLink terms), `local_gemm_ms` (the same-shape GEMM without the
+exchange, same run), `parity_max_rel_err` (sampled output rows of every rank against the CPU oracle,
+outside the timed region), `comparators` (cuBLAS, and cuBLAS + NCCL reduce-scatter for N > 1),
+`cpu_baseline` (N = 1), and the SM clocks sampled while the timed steps ran.
 
---impl reference times the CPU restatement of the upstream torch reference path
-(oracle/) on the host cores with every thread torch can use, same workload and metric,
-each step a bounded sample.
+At N = 1 the line also has `extra`: one sub-record per remaining benchmark configuration (INT8
+1024^3 and 8192^3, FP8 row-scaled, FP8 128-block-scaled, MXFP8 8192^3 and the skinny M = 16/64/128
+shapes, NVFP4 8192^3, BF16 8192^3, the NVFP4 / MXFP8 / row-wise quantizers in GB/s, FP8-QK causal
+attention), each with its own kernel time, roofline, clock samples and library comparators
+(`torch.mm`, `torch._int_mm`, `torch._scaled_mm`, SDPA) timed interleaved in the same process.
+--workload NAME makes NAME the main line instead (no extras).
+
+--impl reference times the CPU restatement of the upstream torch reference path (oracle/) on the
+host cores with every thread torch can use, same workload and metric, each step a bounded sample.
 """
 
 from __future__ import annotations
@@ -46,26 +49,41 @@ SEED_MM = 2025 * 2024 + 2027  # upstream benchmark_mm.py:36
 SEED_ATTN = 2025 * 2026  # upstream benchmark_attn.py:66
 L2_BYTES = 126 * 2**20
 SPEC_BF16_TFLOPS = 2250.0
-# dense tensor-core rate of each kind relative to bf16 (B200: fp8/int8 2x, fp4 4x)
-RATE_VS_BF16 = {"mxfp8": 2.0, "nvfp4": 4.0, "int8": 2.0, "bf16": 1.0}
+NVLINK_GBS_MEASURED = 770.0  # peer copy per direction per GPU measured on this pool (nominal 900)
+NVLINK_GBS_NOMINAL = 900.0
+# dense tensor-core rate of each arithmetic kind relative to bf16 (B200: fp8/int8 2x, fp4 4x)
+RATE_VS_BF16 = {"mxfp8": 2.0, "nvfp4": 4.0, "int8": 2.0, "bf16": 1.0, "fp8": 2.0}
 
 # name -> (family, metric, shape)
 WORKLOADS = {
+    "bf16_gemm_rs": ("rs", "BF16 GEMM + reduce-scatter TFLOPS at M=N=8192, K=28672 sharded over the ranks", (8192, 8192, 28672)),
     "mxfp8_gemm_8192": ("gemm", "MXFP8 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
     "nvfp4_gemm_8192": ("gemm", "NVFP4 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
     "int8_gemm_8192": ("gemm", "row-scaled INT8 GEMM TOPS at M=N=K=8192", (8192, 8192, 8192)),
     "int8_gemm_1024": ("gemm", "row-scaled INT8 GEMM TOPS at M=N=K=1024", (1024, 1024, 1024)),
+    "fp8_gemm_8192": ("gemm", "row-scaled FP8 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
+    "fp8_block128_gemm_8192": ("gemm", "FP8 GEMM with 1x128 / 128x128 block scales, TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
     "bf16_gemm_8192": ("gemm", "BF16 GEMM TFLOPS at M=N=K=8192", (8192, 8192, 8192)),
     "mxfp8_gemm_m16": ("gemm", "MXFP8 GEMM TFLOPS at M=16, N=K=8192", (16, 8192, 8192)),
     "mxfp8_gemm_m64": ("gemm", "MXFP8 GEMM TFLOPS at M=64, N=K=8192", (64, 8192, 8192)),
     "mxfp8_gemm_m128": ("gemm", "MXFP8 GEMM TFLOPS at M=128, N=K=8192", (128, 8192, 8192)),
-    "bf16_gemm_rs": ("rs", "BF16 GEMM + reduce-scatter TFLOPS at M=N=8192, K=28672 sharded over the ranks", (8192, 8192, 28672)),
     "nvfp4_quant_8192": ("quant", "NVFP4 quantizer GB/s at 8192x8192 bf16", (8192, 8192)),
+    "mxfp8_quant_8192": ("quant", "MXFP8 quantizer GB/s at 8192x8192 bf16", (8192, 8192)),
+    "rowwise_quant_attn": ("quant", "row-wise E4M3 quantizer GB/s on Q of the attention configuration (524288 rows of 128)", (4 * 4096 * 32, 128)),
     "attn_fp8_causal": ("attn", "FP8-QK causal GQA attention TFLOPS (B=4, Hq=32, Hkv=8, L=4096, D=128)", (4, 4096, 32, 8, 128)),
 }
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures
-# under profiles/; None where no capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"mxfp8_gemm_8192": 356.7e6 + 117.0e6, "attn_fp8_causal": 120.2e6 + 88.1e6, "nvfp4_quant_8192": 134.2e6 + 20.4e6}
+DEFAULT_WORKLOAD = "bf16_gemm_rs"
+EXTRA_WORKLOADS = [
+    "int8_gemm_1024", "int8_gemm_8192", "fp8_gemm_8192", "fp8_block128_gemm_8192", "mxfp8_gemm_8192", "mxfp8_gemm_m16", "mxfp8_gemm_m64",
+    "mxfp8_gemm_m128", "nvfp4_gemm_8192", "bf16_gemm_8192", "nvfp4_quant_8192", "mxfp8_quant_8192", "rowwise_quant_attn", "attn_fp8_causal",
+]
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the
+# one-kernel ncu captures summarised under profiles/ (file named beside each figure)
+NCU_TRAFFIC = {
+    "mxfp8_gemm_8192": (356.7e6 + 117.0e6, "profiles/gemm_mxfp8_8192_2cta.md"),
+    "attn_fp8_causal": (120.2e6 + 88.1e6, "profiles/attn_fwd_fp8_causal_b4_l4096.md"),
+    "nvfp4_quant_8192": (134.2e6 + 20.4e6, "profiles/quant_nvfp4_8192x8192.md"),
+}
 
 
 def load_peaks():
@@ -78,12 +96,13 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the GPU is loaded."""
+    """Samples SM clocks and throttle reasons with nvidia-smi (read-only query) while the GPU is loaded.
+    One sampler runs for the whole process; window() picks the samples of a time interval."""
 
     Q = "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.path = index, None, None
+    def __init__(self, index: int, period_ms: int = 50):
+        self.index, self.proc, self.path, self.period_ms = index, None, None, period_ms
 
     def start(self):
         try:
@@ -91,24 +110,16 @@ class ClockSampler:
             os.close(fd)
             self.fh = open(self.path, "w")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                 stdout=self.fh, stderr=subprocess.DEVNULL,
             )
         except Exception:
             self.proc = None
 
-    def stop(self, t_begin: float, t_end: float) -> dict:
-        """Median SM clock over the samples whose timestamp lies in [t_begin, t_end] (wall clock)."""
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.fh.close()
+    def _rows(self):
         rows = []
+        if self.path is None or not os.path.exists(self.path):
+            return rows
         with open(self.path) as fh:
             for line in fh:
                 f = [x.strip() for x in line.split(",")]
@@ -120,11 +131,21 @@ class ClockSampler:
                 except ValueError:
                     continue
                 rows.append((ts, clk, cmax, f[5:9]))
-        os.unlink(self.path)
+        return rows
+
+    def window(self, t_begin: float, t_end: float) -> dict:
+        """Median SM clock over the samples whose timestamp lies in [t_begin, t_end] (wall clock)."""
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        try:
+            self.fh.flush()
+        except Exception:
+            pass
+        rows = self._rows()
         inside = [r for r in rows if t_begin <= r[0] <= t_end]
         if not inside and rows:
-            # a timed region shorter than the sampling period: the sample nearest to it (the untimed
-            # lead-in keeps the GPU under the same load right before), with its distance stated
+            # a region shorter than the sampling period: the sample nearest to it, with its distance stated
             near = min(rows, key=lambda r: min(abs(r[0] - t_begin), abs(r[0] - t_end)))
             inside = [near]
             out["nearest_sample_ms_from_timed_region"] = round(1e3 * min(abs(near[0] - t_begin), abs(near[0] - t_end)), 1)
@@ -138,14 +159,35 @@ class ClockSampler:
                        samples=len(inside))
         return out
 
+    def stop(self, t_begin: float | None = None, t_end: float | None = None) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        if t_begin is not None:
+            out = self.window(t_begin, t_end)
+        self.fh.close()
+        if self.path and os.path.exists(self.path):
+            os.unlink(self.path)
+        self.proc = None
+        return out
+
 
 def _pin(t: torch.Tensor) -> torch.Tensor:
     p = torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory()
-    if t.element_size() == 1:
-        p.view(torch.uint8).copy_(t.view(torch.uint8))
-    else:
-        p.copy_(t)
+    _copy(p, t)
     return p
+
+
+def _copy(dst: torch.Tensor, src: torch.Tensor, non_blocking: bool = False) -> None:
+    if dst.element_size() == 1:  # 8-bit float dtypes: copy the bytes
+        dst.view(torch.uint8).copy_(src.view(torch.uint8), non_blocking=non_blocking)
+    else:
+        dst.copy_(src, non_blocking=non_blocking)
 
 
 def _nbytes(ts) -> int:
@@ -153,11 +195,11 @@ def _nbytes(ts) -> int:
 
 
 # ------------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm: workloads
 # ------------------------------------------------------------------------------------------
-def build_gpu_workload(name: str, dev: torch.device) -> dict:
-    """Operands resident on `dev`; returns step() (C ABI, preallocated outputs), host_step()
-    (public API from pinned host buffers, result read back) and the accounting."""
+def build_gpu_workload(name: str, dev: torch.device, timeout_ms: int = 2000) -> dict:
+    """Operands resident on `dev`.  Returns step() (C ABI, preallocated outputs), api (the public
+    Python call on device tensors), comparators (library calls of the same problem) and the accounting."""
     import gn_kernels_b200 as gk
     from gn_kernels_b200 import _lib, ops
 
@@ -166,7 +208,7 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
     P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
     stream = lambda: ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)  # noqa: E731
     kind = name.split("_")[0]
-    w = {"family": family, "metric": metric, "kind": kind, "config": {}}
+    w = {"name": name, "family": family, "metric": metric, "kind": kind, "config": {}, "comparators": {}, "dtype": kind}
 
     if family == "gemm":
         M, N, K = shape
@@ -174,13 +216,32 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
         A = torch.randn(M, K, generator=g, dtype=torch.float32).to(dev)
         Bt = torch.randn(N, K, generator=g, dtype=torch.float32).to(dev)
         C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-        if kind == "mxfp8":
+        if name == "fp8_block128_gemm_8192":
+            # DeepSeek-style operands: E4M3 codes, fp32 scale per (row, 128 K) of A and per 128 x 128 block of B
+            Aq, Bq = A.to(torch.float8_e4m3fn), Bt.to(torch.float8_e4m3fn)
+            sfa = (torch.rand(K // 128, M, generator=g) + 0.5).to(dev)  # M-major: element (m, kb) at kb * M + m
+            sfb = (torch.rand(N // 128, K // 128, generator=g) + 0.5).to(dev)
+            step = lambda: L.gnk_mm_f8_block128(P(Aq), K, P(sfa), M, P(Bq), K, P(sfb), K // 128, None, None, 0, P(C), N, M, N, K, stream())  # noqa: E731
+            ins = [Aq, Bq, sfa, sfb]
+            api = lambda a, b, sa, sb: gk.cutedsl.sm120.sm120_mm_fp8_1d2d.mm(a, sa.T, b, sb)  # noqa: E731
+            algo_bytes = (M + N) * K + 2 * M * N
+            w["kind"] = w["dtype"] = "fp8"
+            sfa_mk = sfa.T.contiguous()  # [M, K/128] row-major for the library comparator
+
+            def cublaslt_blockwise():
+                from torch.nn.functional import ScalingType, SwizzleType, scaled_mm  # noqa: F401
+
+                return scaled_mm(Aq, Bq.T, sfa_mk, ScalingType.BlockWise1x128, sfb, ScalingType.BlockWise128x128, output_dtype=torch.bfloat16)
+
+            w["comparators"]["cuBLASLt blockwise (F.scaled_mm 1x128 / 128x128)"] = cublaslt_blockwise
+        elif kind == "mxfp8":
             Aq, sfa = gk.quantize_mx(A.bfloat16(), torch.float8_e4m3fn, swizzled_scales=True)
             Bq, sfb = gk.quantize_mx(Bt.bfloat16(), torch.float8_e4m3fn, swizzled_scales=True)
             step = lambda: L.gnk_mm_mxfp8(P(Aq), K, P(Bq), K, P(sfa), P(sfb), P(C), N, M, N, K, stream())  # noqa: E731
             ins = [Aq, Bq, sfa, sfb]
             api = lambda a, b, sa, sb: gk.cutedsl.sm100.sm100_mm_mxfp8.mm(a, b, sa, sb)  # noqa: E731
             algo_bytes = N * K + N * K // 32 + M * K + M * K // 32 + 2 * M * N
+            w["comparators"]["cuBLASLt MXFP8 (torch._scaled_mm)"] = lambda: torch._scaled_mm(Aq, Bq.T, sfa, sfb, out_dtype=torch.bfloat16)
         elif kind == "nvfp4":
             tsa, tsb = ops.absmax(A, 2688.0), ops.absmax(Bt, 2688.0)
             Aq, sfa = gk.quantize_nvfp4_triton(A.bfloat16(), tsa)
@@ -190,6 +251,9 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
             ins = [Aq, Bq, sfa, sfb]
             api = lambda a, b, sa, sb: gk.cutedsl.sm100.sm100_mm_nvfp4.mm(a, b, sa, sb, alpha)  # noqa: E731
             algo_bytes = (M + N) * (K // 2 + K // 16) + 2 * M * N
+            w["comparators"]["cuBLASLt NVFP4 (torch._scaled_mm)"] = lambda: torch._scaled_mm(
+                Aq.view(torch.float4_e2m1fn_x2), Bq.view(torch.float4_e2m1fn_x2).T, sfa.view(torch.float8_e4m3fn), sfb.view(torch.float8_e4m3fn),
+                out_dtype=torch.bfloat16)
         elif kind == "int8":
             Aq, sA = gk.quantize_rowwise(A, torch.int8)
             Bq, sB = gk.quantize_rowwise(Bt, torch.int8)
@@ -198,12 +262,25 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
             ins = [Aq, Bq, sA, sB]
             api = lambda a, b, sa, sb: gk.triton_mm(a, b.T, scale_A=sa, scale_B=sb)  # noqa: E731
             algo_bytes = (M + N) * K + 2 * M * N
+            Ci = torch.empty(M, N, dtype=torch.int32, device=dev)
+            w["comparators"]["cuBLAS INT8 (torch._int_mm, int32 out, no scaling)"] = lambda: torch._int_mm(Aq, Bq.T, out=Ci)
+        elif kind == "fp8":
+            Aq, sA = gk.quantize_rowwise(A, torch.float8_e4m3fn)
+            Bq, sB = gk.quantize_rowwise(Bt, torch.float8_e4m3fn)
+            sA, sB = sA.view(M, 1), sB.view(1, N)
+            step = lambda: L.gnk_mm_f8(P(Aq), K, P(Bq), K, P(C), N, M, N, K, P(sA), P(sB), None, stream())  # noqa: E731
+            ins = [Aq, Bq, sA, sB]
+            api = lambda a, b, sa, sb: gk.triton_mm(a, b.T, scale_A=sa, scale_B=sb)  # noqa: E731
+            algo_bytes = (M + N) * K + 2 * M * N
+            w["comparators"]["cuBLASLt FP8 row-scaled (torch._scaled_mm)"] = lambda: torch._scaled_mm(Aq, Bq.T, sA, sB, out_dtype=torch.bfloat16)
         else:
             Ab, Bb = A.bfloat16(), Bt.bfloat16()
             step = lambda: L.gnk_mm_bf16(P(Ab), K, P(Bb), K, P(C), N, M, N, K, stream())  # noqa: E731
             ins = [Ab, Bb]
             api = lambda a, b: gk.cutedsl.sm100.sm100_mm_bf16.mm(a, b.T)  # noqa: E731
             algo_bytes = 2 * (M + N) * K + 2 * M * N
+            w["comparators"]["cuBLAS BF16 (torch.mm)"] = lambda: torch.mm(Ab, Bb.T, out=C)
+        del A, Bt
         w.update(work=2.0 * M * N * K, unit="TOP/s" if kind == "int8" else "TFLOP/s", scale=1e12, ins=ins, outs=[C], api=api, step=step,
                  algo_bytes=algo_bytes, bound="hbm" if M <= 128 else "tensor", config={"M": M, "N": N, "K": K})
     elif family == "rs":
@@ -219,6 +296,7 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
         x = (torch.randn(M, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)
         wt = (torch.randn(N, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)
         out = torch.empty(M // world, N, dtype=torch.bfloat16, device=dev)
+        full = torch.empty(M, N, dtype=torch.bfloat16, device=dev)  # the local GEMM without exchange writes here
         path = "single GPU: plain GEMM"
         if world > 1:
             import torch.distributed._symmetric_memory as symm_mem
@@ -230,34 +308,66 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
             flags = symm_mem.empty(flag_words(M, N, world), dtype=torch.int32, device=dev)
             flags.zero_()
             fh = symm_mem.rendezvous(flags, dist.group.WORLD)
+            torch.cuda.synchronize(dev)
             dist.barrier()
-            path = "pull through the NVLink multicast address (multimem.ld_reduce)" if getattr(ph, "multicast_ptr", 0) else "push by peer stores"
+            path = "pull: multimem.ld_reduce on the NVLink multicast address" if getattr(ph, "multicast_ptr", 0) else "push: bulk stores into the owner's slots"
 
             def step():
-                gemm_rs(x, wt, partial, ph, out, flags, fh)
+                gemm_rs(x, wt, partial, ph, out, flags, fh, timeout_ms=timeout_ms)
                 return 0
 
-            api = lambda a, b: gemm_rs(a, b, partial, ph, out, flags, fh)  # noqa: E731
+            def api(a, b):
+                o = torch.empty_like(out)
+                return gemm_rs(a, b, partial, ph, o, flags, fh, timeout_ms=timeout_ms)
+
+            def cublas_nccl():
+                torch.mm(x, wt.T, out=full)
+                dist.reduce_scatter_tensor(out, full)
+
+            w["comparators"]["cuBLAS BF16 GEMM + NCCL reduce_scatter (unfused, one stream)"] = cublas_nccl
             w["extra_resident"] = partial.numel() * 2
         else:
             step = lambda: L.gnk_mm_bf16(P(x), Kl, P(wt), Kl, P(out), N, M, N, Kl, stream())  # noqa: E731
             api = lambda a, b: gk.cutedsl.sm100.sm100_mm_bf16.mm(a, b.T)  # noqa: E731
-        w.update(work=2.0 * M * N * Kt / world, unit="TFLOP/s", scale=1e12, ins=[x, wt], outs=[out], api=api, step=step, kind="bf16",
-                 algo_bytes=2 * (M + N) * Kl + 2 * M * N, bound="tensor", scaling="strong",
-                 config={"M": M, "N": N, "K_total": Kt, "K_per_rank": Kl, "data_path": path,
+            w["comparators"]["cuBLAS BF16 (torch.mm)"] = lambda: torch.mm(x, wt.T, out=full)
+        w["local_gemm"] = lambda: L.gnk_mm_bf16(P(x), Kl, P(wt), Kl, P(full), N, M, N, Kl, stream())
+        w["parity_inputs"] = (x, wt, out)
+        w.update(work=2.0 * M * N * Kt / world, unit="TFLOP/s", scale=1e12, ins=[x, wt], outs=[out], api=api, step=step, kind="bf16", dtype="bf16",
+                 algo_bytes=2 * (M + N) * Kl + 2 * M * N, bound="tensor", scaling="strong", world=world,
+                 nvlink_bytes=(world - 1) * M * N * 2 // world,
+                 config={"M": M, "N": N, "K_total": Kt, "K_per_rank": Kl, "data_path": path, "timeout_ms": timeout_ms,
                          "nvlink_bytes_per_rank": (world - 1) * M * N * 2 // world})
     elif family == "quant":
         M, K = shape
         g = torch.Generator(device="cpu").manual_seed(SEED_MM)
         x = torch.randn(M, K, generator=g, dtype=torch.float32).bfloat16().to(dev)
-        ts = ops.absmax(x, 2688.0)
-        q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
-        sf = torch.empty(M, K // 16, dtype=torch.uint8, device=dev)
-        step = lambda: L.gnk_quant_nvfp4(P(x), 0, M, K, K, P(ts), 1e-12, P(q), P(sf), 1, stream())  # noqa: E731
-        api = lambda xx: gk.quantize_nvfp4_triton(xx, ts)[0]  # noqa: E731
-        nbytes = 2 * M * K + M * K // 2 + M * K // 16
+        if kind == "nvfp4":
+            ts = ops.absmax(x, 2688.0)
+            q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+            sf = torch.empty(M, K // 16, dtype=torch.uint8, device=dev)
+            step = lambda: L.gnk_quant_nvfp4(P(x), 0, M, K, K, P(ts), 1e-12, P(q), P(sf), 1, stream())  # noqa: E731
+            api = lambda xx: gk.quantize_nvfp4_triton(xx, ts)[0]  # noqa: E731
+            nbytes = 2 * M * K + M * K // 2 + M * K // 16
+            cfg = {"M": M, "K": K, "tensor_scale": "precomputed amax/(6*448), not in the timed step"}
+        elif kind == "mxfp8":
+            q = torch.empty(M, K, dtype=torch.uint8, device=dev)
+            sf = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+            step = lambda: L.gnk_quant_mx(P(x), 0, M, K, K, 1, 0, P(q), P(sf), 1, stream())  # noqa: E731
+            api = lambda xx: gk.quantize_mx(xx, torch.float8_e4m3fn, swizzled_scales=True)[0]  # noqa: E731
+            nbytes = 2 * M * K + M * K + M * K // 32
+            cfg = {"M": M, "K": K}
+        else:
+            q = torch.empty(M, K, dtype=torch.uint8, device=dev)
+            sf = torch.empty(M, dtype=torch.float32, device=dev)
+            step = lambda: L.gnk_quant_rowwise(P(x), 0, M, K, K, 1, P(q), P(sf), 0, 0, stream())  # noqa: E731
+            api = lambda xx: gk.quantize_rowwise(xx, torch.float8_e4m3fn)[0]  # noqa: E731
+            nbytes = 2 * M * K + M * K + 4 * M
+            cfg = {"rows": M, "cols": K}
+        dst = torch.empty(nbytes // 2, dtype=torch.uint8, device=dev)
+        src = torch.empty(nbytes // 2, dtype=torch.uint8, device=dev)
+        w["comparators"]["device copy moving the same number of bytes (torch copy_)"] = lambda: dst.copy_(src)
         w.update(work=float(nbytes), unit="GB/s", scale=1e9, ins=[x], outs=[q, sf], api=api, step=step, algo_bytes=nbytes, bound="hbm",
-                 config={"M": M, "K": K, "tensor_scale": "precomputed amax/(6*448), not in the timed step"})
+                 config=cfg, dtype="f32")
     else:
         B, Lq, Hq, Hkv, D = shape
         g = torch.Generator(device="cpu").manual_seed(SEED_ATTN)
@@ -271,21 +381,64 @@ def build_gpu_workload(name: str, dev: torch.device) -> dict:
         st = [I3(*t.stride()[:3]) for t in (qq, kq, v, o)]
         step = lambda: L.gnk_attn_fwd(P(qq), P(kq), P(v), P(o), P(sq), P(sk), 1, B, Lq, Lq, Hq, Hkv, D, st[0], st[1], st[2], st[3], 1, stream())  # noqa: E731
         api = lambda a, b, c, d, e: gk.triton_attn(a, b, c, d, e, causal=True)  # noqa: E731
+        qt, kt, vt = qf.transpose(1, 2), kf.transpose(1, 2), v.transpose(1, 2)  # [B, H, L, D] views for SDPA
+        w["comparators"]["torch SDPA bf16 causal GQA (library flash attention, unquantised QK)"] = lambda: torch.nn.functional.scaled_dot_product_attention(
+            qt, kt, vt, is_causal=True, enable_gqa=True)
         w.update(work=4.0 * B * Hq * Lq * Lq * D / 2, unit="TFLOP/s", scale=1e12, ins=[qq, kq, v, sq, sk], outs=[o], api=api, step=step,
-                 algo_bytes=_nbytes([qq, kq, v, sq, sk, o]), bound="tensor",
+                 algo_bytes=_nbytes([qq, kq, v, sq, sk, o]), bound="tensor", dtype="fp8",
                  config={"B": B, "L": Lq, "Hq": Hq, "Hkv": Hkv, "D": D, "causal": True, "flops": "causal half of 4*B*Hq*L*L*D"})
 
-    pinned = [_pin(t) for t in w["ins"]]
-    out0 = w["outs"][0]
-    out_host = torch.empty(out0.shape, dtype=out0.dtype).pin_memory()
-
-    def host_step():
-        dev_in = [p.to(dev, non_blocking=True) for p in pinned]
-        out = w["api"](*dev_in)
-        out_host.copy_(out.view(out_host.dtype) if out.dtype != out_host.dtype else out, non_blocking=True)
-
-    w.update(host_step=host_step, h2d=_nbytes(pinned), d2h=_nbytes([out_host]), resident_bytes=_nbytes(w["ins"]) + _nbytes(w["outs"]) + w.get("extra_resident", 0))
+    w["resident_bytes"] = _nbytes(w["ins"]) + _nbytes(w["outs"]) + w.get("extra_resident", 0)
     return w
+
+
+class HostPipeline:
+    """End-to-end step through the public API from pinned host buffers: the inputs go host -> device,
+    the op runs, the result comes device -> host.  Two input buffers and separate copy streams let the
+    copy-in of step i+1 and the copy-out of step i-1 overlap the kernel of step i (PCIe is full duplex);
+    every byte of every step is still copied inside the timed region."""
+
+    def __init__(self, w: dict, dev: torch.device):
+        self.w, self.dev = w, dev
+        self.pinned = [_pin(t) for t in w["ins"]]
+        out0 = w["outs"][0]
+        self.out_host = [torch.empty(out0.shape, dtype=out0.dtype).pin_memory() for _ in range(2)]
+        self.dev_in = [[torch.empty_like(t) for t in w["ins"]] for _ in range(2)]
+        self.s_in, self.s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]
+        self.ev_free = [torch.cuda.Event() for _ in range(2)]
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]
+        self.i = 0
+        self.h2d = _nbytes(self.pinned)
+        self.d2h = _nbytes([self.out_host[0]])
+
+    def step(self):
+        b = self.i & 1
+        comp = torch.cuda.current_stream(self.dev)
+        with torch.cuda.stream(self.s_in):
+            if self.i >= 2:
+                self.s_in.wait_event(self.ev_free[b])  # the kernel that last read this buffer has finished
+            for d, p in zip(self.dev_in[b], self.pinned):
+                _copy(d, p, non_blocking=True)
+            self.ev_in[b].record(self.s_in)
+        comp.wait_event(self.ev_in[b])
+        out = self.w["api"](*self.dev_in[b])
+        self.ev_free[b].record(comp)
+        done = torch.cuda.Event()
+        done.record(comp)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(done)
+            if self.i >= 2:
+                self.s_out.wait_event(self.ev_out[b])
+            _copy(self.out_host[b], out, non_blocking=True)
+            out.record_stream(self.s_out)
+            self.ev_out[b].record(self.s_out)
+        self.i += 1
+
+    def drain(self):
+        comp = torch.cuda.current_stream(self.dev)
+        comp.wait_stream(self.s_in)
+        comp.wait_stream(self.s_out)
 
 
 # ------------------------------------------------------------------------------------------
@@ -304,7 +457,13 @@ def build_cpu_workload(name: str, rows: int):
         g = torch.Generator(device="cpu").manual_seed(SEED_MM)
         A = torch.randn(M, K, generator=g, dtype=torch.float32)[:rows]
         Bt = torch.randn(N, K, generator=g, dtype=torch.float32)
-        if kind == "mxfp8":
+        if name == "fp8_block128_gemm_8192":
+            Aq = A.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+            Bq = Bt.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+            sfa = torch.rand(rows, K // 128, generator=g) + 0.5
+            sfb = torch.rand(N // 128, K // 128, generator=g) + 0.5
+            step = lambda: omm.mm_f8_block128(Aq, sfa, Bq, sfb)  # noqa: E731
+        elif kind == "mxfp8":
             Aq, sfa = oq.quantize_mx(A.bfloat16().float().numpy(), "e4m3")
             Bq, sfb = oq.quantize_mx(Bt.bfloat16().float().numpy(), "e4m3")
             step = lambda: omm.mm_mxfp8(Aq, Bq, sfa, sfb)  # noqa: E731
@@ -316,6 +475,10 @@ def build_cpu_workload(name: str, rows: int):
             Aq, sA = oq.quantize_rowwise(A.numpy(), "int8")
             Bq, sB = oq.quantize_rowwise(Bt.numpy(), "int8")
             step = lambda: omm.mm_i8_row_scaled(Aq, Bq, sA, sB)  # noqa: E731
+        elif kind == "fp8":
+            Aq, sA = oq.quantize_rowwise(A.numpy(), "e4m3")
+            Bq, sB = oq.quantize_rowwise(Bt.numpy(), "e4m3")
+            step = lambda: omm.mm_f8_row_scaled(Aq, Bq, sA, sB)  # noqa: E731
         else:
             Ab, Bb = A.bfloat16(), Bt.bfloat16()
             step = lambda: omm.mm_bf16(Ab, Bb)  # noqa: E731
@@ -323,12 +486,20 @@ def build_cpu_workload(name: str, rows: int):
         return step, 2.0 * rows * N * K, sample
     if family == "quant":
         M, K = shape
-        rows = min(rows, M)
+        rows = min(rows, M) if kind != "rowwise" else min(rows * 64, M)
         g = torch.Generator(device="cpu").manual_seed(SEED_MM)
-        x = torch.randn(M, K, generator=g, dtype=torch.float32)[:rows].bfloat16().float().numpy()
-        ts = np.float32(np.abs(x).max() / 2688.0)
-        step = lambda: oq.quantize_nvfp4(x, ts)  # noqa: E731
-        return step, float(2 * rows * K + rows * K // 2 + rows * K // 16), f"{rows} of {M} rows (numpy restatement of quantize_nvfp4)"
+        x = torch.randn(rows, K, generator=g, dtype=torch.float32).bfloat16().float().numpy()
+        if kind == "nvfp4":
+            ts = np.float32(np.abs(x).max() / 2688.0)
+            step = lambda: oq.quantize_nvfp4(x, ts)  # noqa: E731
+            work = float(2 * rows * K + rows * K // 2 + rows * K // 16)
+        elif kind == "mxfp8":
+            step = lambda: oq.quantize_mx(x, "e4m3")  # noqa: E731
+            work = float(3 * rows * K + rows * K // 32)
+        else:
+            step = lambda: oq.quantize_rowwise(x, "e4m3")  # noqa: E731
+            work = float(3 * rows * K + 4 * rows)
+        return step, work, f"{rows} of {M} rows (numpy restatement of the upstream quantizer)"
     B, L, Hq, Hkv, D = shape
     g = torch.Generator(device="cpu").manual_seed(SEED_ATTN)
     heads = 2
@@ -352,7 +523,6 @@ def time_cpu(step, steps: int, warmup: int) -> float:
     return time.perf_counter() - t0
 
 
-# ------------------------------------------------------------------------------------------
 def run_reference(args, rank: int):
     if rank != 0:
         return
@@ -364,20 +534,19 @@ def run_reference(args, rank: int):
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     step, work, sample = build_cpu_workload(args.workload, args.cpu_rows)
     # Keep the whole run within a few minutes whatever --steps says: one probe step; if K steps would
-    # take longer than about five minutes, fewer steps are executed and the line says how many (the
-    # per-step cost is dominated by dequantising the full B operand, so a smaller row sample would
-    # not shorten it).
+    # take longer than about three minutes, fewer steps are executed and the line says how many.
     t_probe = time_cpu(step, 1, 0)
     executed = args.steps
-    if t_probe * args.steps > 300.0:
-        executed = max(2, int(300.0 / t_probe))
+    if t_probe * args.steps > 180.0:
+        executed = max(2, int(180.0 / t_probe))
     total = time_cpu(step, executed, 0) * args.steps / executed
     unit, scale = ("GB/s", 1e9) if family == "quant" else (("TOP/s" if kind == "int8" else "TFLOP/s"), 1e12)
     val = work * args.steps / total / scale
     cores = torch.get_num_threads()
     line = {
         "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if family == "rs" else "weak", "vs_baseline": None, "dtype": kind,
+        "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if family == "rs" else "weak", "vs_baseline": None,
+        "dtype": "bf16" if family == "rs" else kind,
         "data": "synthetic", "config": {"workload": args.workload, "shape": list(shape), "sample": sample},
         "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -386,135 +555,303 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
-def run_gpu(args, rank: int, local_rank: int, world: int):
-    import torch.distributed as dist
+# ------------------------------------------------------------------------------------------
+# GPU arm: measurement
+# ------------------------------------------------------------------------------------------
+class Runner:
+    def __init__(self, args, rank, local_rank, world):
+        import torch.distributed as dist
 
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    from gn_kernels_b200 import _lib
-
-    w = build_gpu_workload(args.workload, dev)
-    step = w["step"]
-    peaks = load_peaks()
-    flush_buf = None
-    if w["resident_bytes"] < 1.5 * L2_BYTES:  # operands could stay in L2 between steps: flush it
-        flush_buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
-
-    def barrier():
+        self.args, self.rank, self.world, self.dist = args, rank, world, dist
+        self.dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(self.dev)
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.peaks = load_peaks()
+        self.sampler = ClockSampler(local_rank)
+        if rank == 0:
+            self.sampler.start()
+        self.flush_buf = None
 
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
-        rc = step()
-        if rc != 0:
-            raise RuntimeError(f"kernel launch failed: status {rc}")
-    _lib.raise_on_device_error()
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize(self.dev)
 
-    # ---- timed region: exactly K steps, one event pair per launch ----
-    ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.15)
-    barrier()
-    # Untimed lead-in of the same launches (about half a second) so that the 100 ms clock sampler
-    # sees the GPU in the loaded state the timed steps run in; the timed region follows at once.
-    t_load0 = time.time()
-    for _ in range(args.lead_in):
-        step()
-    for i in range(args.steps):
-        if flush_buf is not None:
-            flush_buf.zero_()
-        ev0[i].record()
-        step()
-        ev1[i].record()
-    barrier()
-    t_load1 = time.time()
-    per_launch = [a.elapsed_time(b) for a, b in zip(ev0, ev1)]
-    if flush_buf is None:
-        total_ms = ev0[0].elapsed_time(ev1[-1])  # back-to-back launches: the whole region
-    else:
-        total_ms = float(np.sum(per_launch))  # L2 flushes between steps are not part of a step
-    clocks = sampler.stop(t_load0 + 0.1, t_load1) if rank == 0 else None
-    _lib.raise_on_device_error()
+    def max_over_ranks(self, vals):
+        t = torch.tensor(vals, dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t]
 
-    # ---- end to end through the public API from pinned host buffers ----
-    e2e_steps = max(2, min(args.steps, 5))
-    w["host_step"]()
-    barrier()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(e2e_steps):
-        w["host_step"]()
-    t1.record()
-    barrier()
-    e2e_ms = t0.elapsed_time(t1)
+    def flush(self):
+        if self.flush_buf is None:
+            self.flush_buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=self.dev)
+        self.flush_buf.zero_()
 
-    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = float(t[0]), float(t[1])
+    def lead_in_count(self, fn, seconds: float) -> int:
+        """Launch count that keeps the GPU busy for about `seconds`: the same on every rank."""
+        torch.cuda.synchronize(self.dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(self.dev)
+        ms = self.max_over_ranks([e0.elapsed_time(e1) / 3])[0]
+        return int(max(1, min(20000, seconds * 1e3 / max(ms, 1e-3))))
 
-    if rank == 0:
-        kind, unit, scale = w["kind"], w["unit"], w["scale"]
-        value = world * w["work"] * args.steps / (total_ms * 1e-3) / scale
-        e2e_val = world * w["work"] * e2e_steps / (e2e_ms * 1e-3) / scale
-        avg_ms = float(np.mean(per_launch))
-        sustained = args.lead_in >= 200  # a long identical lead-in puts the part in its power-capped steady state
+    def timed(self, fn, steps: int, flush: bool):
+        """K launches, one event pair each.  Returns (ms of the whole region, per-launch ms list)."""
+        ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            if flush:
+                self.flush()
+            ev0[i].record()
+            fn()
+            ev1[i].record()
+        self.barrier()
+        per = [a.elapsed_time(b) for a, b in zip(ev0, ev1)]
+        total = float(np.sum(per)) if flush else ev0[0].elapsed_time(ev1[-1])  # L2 flushes between steps are not part of a step
+        return total, per
+
+    def measure(self, name: str, steps: int, warmup: int, main: bool) -> dict:
+        from gn_kernels_b200 import _lib
+
+        args = self.args
+        w = build_gpu_workload(name, self.dev, args.timeout_ms)
+        step = w["step"]
+        flush = w["resident_bytes"] < 1.5 * L2_BYTES  # operands could stay in L2 between steps: flush it
+        warm = max(warmup, 3)
+        for _ in range(warm):
+            rc = step()
+            if rc != 0:
+                raise RuntimeError(f"{name}: kernel launch failed: status {rc}")
+        _lib.raise_on_device_error()
+
+        # Untimed lead-in of the same launches so that the clock sampler sees the GPU in the loaded
+        # state the timed steps run in; the timed region follows at once.
+        lead = self.lead_in_count(step, args.lead_in_s)
+        self.barrier()
+        t_load0 = time.time()
+        for i in range(lead):
+            step()
+            if (i & 63) == 63:
+                torch.cuda.synchronize(self.dev)
+        self.barrier()
+        total_ms, per = self.timed(step, steps, flush)
+        t_load1 = time.time()
+        _lib.raise_on_device_error()
+        total_ms = self.max_over_ranks([total_ms])[0]
+        clocks = self.sampler.window(t_load0 + 0.1, t_load1) if self.rank == 0 else None
+        avg_ms = float(np.mean(per))
+        rec = {"workload": name, "metric": w["metric"], "unit": w["unit"], "dtype": w["dtype"], "steps": steps, "ms_per_step": total_ms / steps,
+               "kernel_ms": avg_ms, "value": self.world * w["work"] * steps / (total_ms * 1e-3) / w["scale"], "clocks": clocks,
+               "config": {"workload": name, **w["config"], "lead_in_steps": lead,
+                          "l2": (f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB > 126 MB L2 (no flush needed), back-to-back launches"
+                                 if not flush else
+                                 f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB could stay in L2: 252 MiB written between steps, steps timed one by one")}}
+        rec["roofline"] = self.roofline(w, avg_ms, sustained=lead * avg_ms > 200.0)
+        if clocks and clocks.get("sm_mhz"):
+            # throughput follows the SM clock on this power-capped part: time x clock compares runs on different boxes
+            rec["roofline"]["achieved_per_sm_mhz"] = rec["roofline"]["achieved"] / clocks["sm_mhz"]
+
+        # local GEMM of the same shape without the exchange (reduce-scatter workload only), same run
+        if "local_gemm" in w:
+            lg = w["local_gemm"]
+            for _ in range(3):
+                lg()
+            n = self.lead_in_count(lg, min(args.lead_in_s, 0.3))
+            for _ in range(n):
+                lg()
+            self.barrier()
+            lt, _ = self.timed(lg, steps, False)
+            rec["local_gemm_ms"] = self.max_over_ranks([lt / steps])[0]
+            rec["frac_of_local_gemm_rate"] = rec["local_gemm_ms"] / rec["ms_per_step"]
+
+        # library comparators, interleaved with our kernel round by round in this process
+        if w["comparators"] and not args.kernel_only:
+            rec["comparators"] = self.compare(w, flush, min(steps, 20), rounds=5)
+
+        # parity of the reduce-scatter output, outside every timed region
+        if "parity_inputs" in w and not args.kernel_only:
+            rec.update(self.rs_parity(w))
+
+        if main and not args.kernel_only:
+            hp = HostPipeline(w, self.dev)
+            e2e_steps = max(3, min(steps, 8))
+            hp.step()
+            hp.step()
+            hp.drain()
+            self.barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(e2e_steps):
+                hp.step()
+            hp.drain()
+            t1.record()
+            self.barrier()
+            e2e_ms = self.max_over_ranks([t0.elapsed_time(t1)])[0]
+            _lib.raise_on_device_error()
+            rec["e2e"] = {"value": self.world * w["work"] * e2e_steps / (e2e_ms * 1e-3) / w["scale"], "unit": w["unit"], "h2d_bytes_per_step": hp.h2d,
+                          "d2h_bytes_per_step": hp.d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                          "how": "public API on pinned host buffers; copy-in of step i+1 and copy-out of step i-1 overlap the kernel of step i on separate streams"}
+            del hp
+        rec["_w"] = w
+        return rec
+
+    def roofline(self, w: dict, avg_ms: float, sustained: bool) -> dict:
+        peaks = self.peaks
+        traffic = NCU_TRAFFIC.get(w["name"])
         if w["bound"] == "tensor":
             achieved = w["work"] / (avg_ms * 1e-3) / 1e12
             bf16_peak = peaks["bf16_sustained"] if sustained else peaks["bf16"]
-            rate = 4.0 / 3.0 if w["family"] == "attn" else RATE_VS_BF16[kind]
+            rate = 4.0 / 3.0 if w["family"] == "attn" else RATE_VS_BF16[w["kind"]]
             peak = bf16_peak * rate
             why = "FP8 QK^T at 2x + BF16 PV at 1x of equal flops -> 4/3 x" if w["family"] == "attn" else f"{rate:g} x"
-            roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                        "peak_source": f"{why} cuBLAS bf16 {'sustained' if sustained else 'burst'} {bf16_peak} TFLOP/s ({peaks['src']})",
-                        "frac_of_spec": achieved / (SPEC_BF16_TFLOPS * rate), "kernel_ms": avg_ms}
+            r = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                 "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None,
+                 "peak_source": f"{why} cuBLAS bf16 {'sustained' if sustained else 'burst'} {bf16_peak} TFLOP/s ({peaks['src']})",
+                 "frac_of_spec": achieved / (SPEC_BF16_TFLOPS * rate), "kernel_ms": avg_ms}
+            if w["family"] == "rs":
+                # a fused compute + collective kernel is bounded by the slower of the GEMM at the tensor peak and
+                # the bytes that must cross NVLink at the link rate
+                t_gemm = w["work"] / (peak * 1e12) * 1e3
+                t_link = w["nvlink_bytes"] / (NVLINK_GBS_MEASURED * 1e9) * 1e3
+                t_roof = max(t_gemm, t_link)
+                r.update(terms={"gemm_ms_at_tensor_peak": t_gemm, "nvlink_ms_at_770_GBs_measured": t_link,
+                                "nvlink_ms_at_900_GBs_nominal": w["nvlink_bytes"] / (NVLINK_GBS_NOMINAL * 1e9) * 1e3,
+                                "roofline_ms": t_roof, "bound_by": "tensor" if t_gemm >= t_link else "nvlink"},
+                         frac=t_roof / avg_ms, frac_is="max(GEMM time at the tensor peak, NVLink time at the measured link rate) / kernel time")
+            return r
+        achieved = w["algo_bytes"] / (avg_ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None, "algorithmic_bytes": w["algo_bytes"],
+                "peak_source": f"copy bandwidth {peaks['hbm_gbs']} GB/s ({peaks['src']})", "kernel_ms": avg_ms}
+
+    def compare(self, w: dict, flush: bool, n: int, rounds: int) -> dict:
+        """Median per-launch time of our kernel and of each library call, alternating round by round."""
+        out = {}
+        ours = w["step"]
+        for cname, cfn in w["comparators"].items():
+            try:
+                for _ in range(3):
+                    cfn()
+                torch.cuda.synchronize(self.dev)
+            except Exception as exc:  # the library has no kernel for this problem on this box
+                out[cname] = {"unavailable": str(exc).splitlines()[0][:200]}
+                continue
+            mine, theirs = [], []
+            for _ in range(rounds):
+                self.barrier()
+                tm, pm = self.timed(ours, n, flush)
+                tt, pt = self.timed(cfn, n, flush)
+                mine.append(tm / n)
+                theirs.append(tt / n)
+            m, t = self.max_over_ranks([float(np.median(mine)), float(np.median(theirs))])
+            scale = self.world * w["work"] / w["scale"]
+            out[cname] = {"ms": t, "value": scale / (t * 1e-3), "ours_ms_same_rounds": m, "ours_value_same_rounds": scale / (m * 1e-3),
+                          "ours_over_theirs": t / m, "rounds": rounds, "launches_per_round": n}
+        return out
+
+    def rs_parity(self, w: dict) -> dict:
+        """Sampled rows of every rank's output against the CPU oracle (bf16-rounded partials, fp32 sum)."""
+        from oracle import gemm_rs as ors
+        from oracle.mm import max_rel_err
+
+        dist, world, rank = self.dist, self.world, self.rank
+        x, wt, out = w["parity_inputs"]
+        M = x.shape[0]
+        rows_per = M // world
+        per_rank = max(4, 64 // world)
+        gsel = torch.Generator().manual_seed(7)
+        local_rows = torch.sort(torch.randperm(rows_per, generator=gsel)[:per_rank]).values
+        global_rows = torch.cat([local_rows + r * rows_per for r in range(world)]).to(self.dev)
+        out.zero_()
+        self.barrier()
+        rc = w["step"]()
+        self.barrier()
+        xs_rows = x.index_select(0, global_rows).contiguous()
+        mine = out.index_select(0, local_rows.to(self.dev)).contiguous()
+        if world > 1:
+            xs = [torch.empty_like(xs_rows) for _ in range(world)]
+            ws = [torch.empty_like(wt) for _ in range(world)]
+            outs = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(xs, xs_rows)
+            dist.all_gather(ws, wt)
+            dist.all_gather(outs, mine)
         else:
-            achieved = w["algo_bytes"] / (avg_ms * 1e-3) / 1e9
-            roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_bytes": w["algo_bytes"],
-                        "peak_source": f"copy bandwidth {peaks['hbm_gbs']} GB/s ({peaks['src']})", "kernel_ms": avg_ms}
-        cpu_baseline = None  # timed at N = 1 only (the launcher pins ranks to one host thread each)
-        if world == 1:
-            cstep, cwork, sample = build_cpu_workload(args.workload, args.cpu_rows)
-            ctot = time_cpu(cstep, 2, 1)
-            cpu_baseline = {"value": cwork * 2 / ctot / scale, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
-                            "sample": sample + ", 2 timed passes"}
-        cfg = {"workload": args.workload, **w["config"],
-               "parallelism": (f"K sharded over {world} ranks, reduce-scatter along M" if w.get("scaling") == "strong" and world > 1
-                               else "replicas only" if world > 1 else "single GPU"),
-               "l2": (f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB > 126 MB L2 (no flush needed)" if flush_buf is None
-                      else f"operands + output {w['resident_bytes'] / 2**20:.0f} MiB could stay in L2: 252 MiB written between steps, steps timed one by one"),
-               "lead_in_steps": args.lead_in}
-        line = {
-            "metric": w["metric"], "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warm,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": w.get("scaling", "weak"), "vs_baseline": None,
-            "dtype": kind, "data": "synthetic", "config": cfg, "roofline": roofline,
-            "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": w["h2d"], "d2h_bytes_per_step": w["d2h"], "steps": e2e_steps},
-            "gpu_launches": args.steps, "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+            xs, ws, outs = [xs_rows], [wt], [mine]
+        res = {}
+        if rank == 0:
+            torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+            refs = ors.gemm_rs([t.cpu() for t in xs], [t.cpu() for t in ws])  # slices the sampled rows by owner
+            errs = [max_rel_err(o.cpu(), r) for o, r in zip(outs, refs)]
+            res = {"parity_max_rel_err": max(errs), "parity": {"rows_per_rank": per_rank, "ranks": world, "tolerance": 1e-2,
+                                                              "ok": bool(max(errs) <= 1e-2), "rc": int(rc or 0),
+                                                              "checker": "oracle.gemm_rs on the host (sum over ranks of bf16(x_r w_r^T), fp32 adds)"}}
+        self.barrier()
+        return res
+
+    def cpu_baseline(self, name: str, unit: str, scale: float) -> dict:
+        cstep, cwork, sample = build_cpu_workload(name, self.args.cpu_rows)
+        ctot = time_cpu(cstep, 2, 1)
+        return {"value": cwork * 2 / ctot / scale, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample + ", 2 timed passes"}
+
+    def run(self):
+        args, world, rank = self.args, self.world, self.rank
+        main = self.measure(args.workload, args.steps, args.warmup, main=True)
+        w = main.pop("_w")
+        extras = []
+        if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_extra and not args.kernel_only:
+            del w
+            torch.cuda.empty_cache()
+            for name in EXTRA_WORKLOADS:
+                try:
+                    r = self.measure(name, max(20, min(args.steps, 100)), 3, main=False)
+                    r.pop("_w")
+                except Exception as exc:
+                    r = {"workload": name, "error": str(exc)[:300]}
+                extras.append(r)
+                torch.cuda.empty_cache()
+        cpu = None
+        if world == 1 and not args.kernel_only:  # the launcher pins ranks to one host thread each
+            cpu = self.cpu_baseline(args.workload, main["unit"], 1e9 if main["unit"] == "GB/s" else 1e12)
+        if rank == 0:
+            fam = WORKLOADS[args.workload][0]
+            cfg = main["config"]
+            cfg["parallelism"] = (f"K sharded over {world} ranks, reduce-scatter along M" if fam == "rs" and world > 1
+                                  else "replicas only" if world > 1 else "single GPU")
+            line = {
+                "metric": main["metric"], "value": main["value"], "unit": main["unit"], "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "strong" if fam == "rs" else "weak", "vs_baseline": None,
+                "dtype": main["dtype"], "data": "synthetic", "config": cfg, "roofline": main["roofline"], "cpu_baseline": cpu,
+                "e2e": main.get("e2e"), "gpu_launches": args.steps, "clocks": main["clocks"],
+            }
+            for k in ("local_gemm_ms", "frac_of_local_gemm_rate", "parity_max_rel_err", "parity", "comparators"):
+                if k in main:
+                    line[k] = main[k]
+            if extras:
+                line["extra"] = extras
+            print(json.dumps(line), flush=True)
+        self.sampler.stop()
+        if world > 1:
+            self.dist.destroy_process_group()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--lead-in", type=int, default=1000, help="untimed launches right before the timed region (clock sampling)")
-    ap.add_argument("--workload", default="mxfp8_gemm_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--lead-in-s", type=float, default=0.6, help="seconds of untimed identical launches right before the timed region (clock sampling)")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="gnk", choices=["gnk", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=512, help="rows of the CPU sample (bounded host time)")
+    ap.add_argument("--timeout-ms", type=int, default=2000, help="bound of the device-side waits of the reduce-scatter")
+    ap.add_argument("--no-extra", action="store_true", help="main line only")
+    ap.add_argument("--kernel-only", action="store_true", help="timed kernel launches only (for profiler captures): no comparators, parity, e2e, CPU arm, extras")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -524,7 +861,7 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU arm")
-    run_gpu(args, rank, local_rank, world)
+    Runner(args, rank, local_rank, world).run()
 
 
 if __name__ == "__main__":

@@ -54,7 +54,7 @@ _SIGNATURES = {
     "gnk_debug_attn_trace": (c_int, [_P]),
     "gnk_debug_force_tile": (c_int, [c_int]),
     "gnk_debug_staged": (c_int, [c_int]),
-    "gnk_debug_flags": (c_int, [c_int]),
+    "gnk_debug_rs_trace": (c_int, [_P]),
     "gnk_debug_max_clusters": (c_int, [c_int]),
     "gnk_debug_trace": (c_int, [_P]),
 }

@@ -8,6 +8,8 @@ run time) and links the CUDA runtime statically.
 
 from __future__ import annotations
 
+import contextlib
+import fcntl
 import hashlib
 import os
 import shutil
@@ -61,9 +63,29 @@ def is_stale() -> bool:
         return fh.read().strip() != source_digest()
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """Exclusive inter-process lock: ranks started together (torchrun) must not compile into the
+    same object files, or load a library another rank is still writing."""
+    fh = open(LIB_PATH + ".lock", "w")
+    try:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        yield
+    finally:
+        fcntl.flock(fh, fcntl.LOCK_UN)
+        fh.close()
+
+
 def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None) -> str:
     if not force and not is_stale():
         return LIB_PATH
+    with _build_lock():
+        if not force and not is_stale():  # another process built it while this one waited
+            return LIB_PATH
+        return _build_locked(force, verbose, extra_flags)
+
+
+def _build_locked(force: bool, verbose: bool, extra_flags: list[str] | None) -> str:
     nvcc = find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libgnk.so (set NVCC or add it to PATH)")
@@ -92,12 +114,15 @@ def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | N
 
     with ThreadPoolExecutor(max_workers=min(8, len(sources()))) as pool:
         objs = list(pool.map(compile_one, sources()))
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    tmp = LIB_PATH + f".tmp{os.getpid()}"
+    cmd = [nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    with open(STAMP_PATH, "w") as fh:
+    os.replace(tmp, LIB_PATH)  # a process that already mapped the old file keeps it
+    with open(STAMP_PATH + ".tmp", "w") as fh:
         fh.write(source_digest())
+    os.replace(STAMP_PATH + ".tmp", STAMP_PATH)
     return LIB_PATH
 
 

@@ -58,8 +58,57 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
+// Descriptor cache.  A tiled tensor map is a pure function of the arguments it is encoded from, so a
+// map built once for (base, extents, strides, box, type, swizzle) can be handed out again: steady-state
+// callers (the same weights, activations of the same shape in the same buffers) then pay a 128-byte
+// copy under a mutex instead of a driver call per operand.  Direct-mapped, 512 entries.
+namespace {
+struct TmapKey {
+  uint64_t base, dims[4], strides[3];
+  uint32_t box[4], dt, swz, rank, pad;
+  bool operator==(const TmapKey& o) const { return memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapEntry {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapCacheSize = 512;
+TmapEntry g_tmap_cache[kTmapCacheSize];
+std::mutex g_tmap_mutex;
+
+inline uint32_t tmap_slot(const TmapKey& k) {
+  uint64_t h = 1469598103934665603ull;
+  const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+  for (size_t i = 0; i < sizeof(TmapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+  return static_cast<uint32_t>((h ^ (h >> 29)) % kTmapCacheSize);
+}
+bool tmap_lookup(const TmapKey& k, CUtensorMap* out) {
+  TmapEntry& e = g_tmap_cache[tmap_slot(k)];
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  if (!e.used || !(e.key == k)) return false;
+  memcpy(out, &e.map, sizeof(CUtensorMap));
+  return true;
+}
+void tmap_insert(const TmapKey& k, const CUtensorMap* m) {
+  TmapEntry& e = g_tmap_cache[tmap_slot(k)];
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  e.key = k;
+  memcpy(&e.map, m, sizeof(CUtensorMap));
+  e.used = true;
+}
+}  // namespace
+
 int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t cols,
                  uint64_t ld_bytes, uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = reinterpret_cast<uint64_t>(base);
+  key.dims[0] = cols; key.dims[1] = rows;
+  key.strides[0] = ld_bytes;
+  key.box[0] = box_cols; key.box[1] = box_rows;
+  key.dt = static_cast<uint32_t>(dt); key.swz = static_cast<uint32_t>(swz); key.rank = 2;
+  if (tmap_lookup(key, map)) return GNK_OK;
   auto fn = encode_fn();
   if (!fn) {
     snprintf(tl_cuda_error, sizeof(tl_cuda_error), "cuTensorMapEncodeTiled entry point not found");
@@ -78,11 +127,19 @@ int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uin
              (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld_bytes, box_rows, box_cols);
     return GNK_ERR_CUDA;
   }
+  tmap_insert(key, map);
   return GNK_OK;
 }
 
 int make_tmap_4d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, const uint64_t dims[4],
                  const uint64_t strides_bytes[3], const uint32_t box[4], CUtensorMapSwizzle swz) {
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = reinterpret_cast<uint64_t>(base);
+  for (int i = 0; i < 4; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i < 3; ++i) key.strides[i] = strides_bytes[i];
+  key.dt = static_cast<uint32_t>(dt); key.swz = static_cast<uint32_t>(swz); key.rank = 4;
+  if (tmap_lookup(key, map)) return GNK_OK;
   auto fn = encode_fn();
   if (!fn) {
     snprintf(tl_cuda_error, sizeof(tl_cuda_error), "cuTensorMapEncodeTiled entry point not found");
@@ -101,6 +158,7 @@ int make_tmap_4d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, con
     snprintf(tl_cuda_error, sizeof(tl_cuda_error), "cuTensorMapEncodeTiled (rank 4) failed (%d)", (int)r);
     return GNK_ERR_CUDA;
   }
+  tmap_insert(key, map);
   return GNK_OK;
 }
 

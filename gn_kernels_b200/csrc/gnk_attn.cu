@@ -16,6 +16,7 @@
 //   warp 9     producer: TMA loads of both Q tiles (once), K and V tiles (2-stage rings)
 // TMEM: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512).
 // Every barrier wait is bounded (see mbar_wait); no thread ever spins without a limit.
+#include <atomic>
 #include <type_traits>
 
 #include "gnk_common.cuh"
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t p_row = sm_p + t * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
     float m_used = -1e38f, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < nt && ok; ++j) {
+    for (int j = 0; j < nt; ++j) {
       long long* tr = (a.trace && blockIdx.x == 0 && (warp & 3) == 0 && lane == 0 && j < 32) ? a.trace + (t * 32 + j) * 8 : nullptr;
       if (tr) tr[0] = clock64();
       // stage the tile's key scales (one per thread of this group), 0 beyond the sequence
@@ -245,7 +246,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         sk[r] = v;
         asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
       }
-      if (!mbar_wait(bar_sfull(t), j & 1, (0x13u << 24) | (1u << 16) | j)) { ok = false; break; }
+      // A wait that runs out does not leave the loop: the four warps of the group meet at the named
+      // barrier above every iteration, so a warp that left alone would strand the other three there.
+      // It stops waiting instead (every later wait is skipped), keeps arriving, and the rows it owns
+      // are written as zeros at the end; the status word tells the host.
+      if (ok && !mbar_wait(bar_sfull(t), j & 1, (0x13u << 24) | (1u << 16) | j)) ok = false;
       tc_fence_after();
       if (tr) tr[1] = clock64();
       const int col0 = j * kBN;
@@ -281,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool grow = mt > m_used + kLazyRescale;
       const bool rescale = __any_sync(0xffffffffu, grow) || j == 0;
       // O and the P buffer may only be touched once the previous P*V of this tile has retired
-      if (j > 0 && !mbar_wait(bar_pvdone(t), (j - 1) & 1, (0x13u << 24) | (2u << 16) | j)) { ok = false; break; }
+      if (j > 0 && ok && !mbar_wait(bar_pvdone(t), (j - 1) & 1, (0x13u << 24) | (2u << 16) | j)) ok = false;
       if (rescale) {
         const float alpha = fast_exp2(m_used - mt);
         m_used = mt;
@@ -387,7 +392,7 @@ GNK_DEFINE_STATUS_READER(attn_status_reader)
 using namespace gnk;
 
 namespace {
-long long* g_attn_trace = nullptr;
+std::atomic<long long*> g_attn_trace{nullptr};
 }
 // Test hook: device buffer of 2 * 32 * 8 int64 receiving clock64 stamps (see AttnArgs::trace); NULL = off.
 extern "C" int gnk_debug_attn_trace(void* device_buffer) {
@@ -427,7 +432,7 @@ extern "C" int gnk_attn_fwd(const void* q, const void* k, const void* v, void* o
   if ((rc = make(&tm_v, v, Lk, Hkv, v_strides, 2, 64, kBN, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)) != GNK_OK) return rc;
 
   AttnArgs a{};
-  a.trace = g_attn_trace;
+  a.trace = g_attn_trace.load();
   a.Lq = static_cast<int>(Lq);
   a.Lk = static_cast<int>(Lk);
   a.Hq = static_cast<int>(Hq);

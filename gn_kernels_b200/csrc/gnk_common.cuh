@@ -78,6 +78,10 @@ static __device__ unsigned int g_dev_status[2];
 __device__ __forceinline__ void report_timeout(uint32_t detail) {
   if (atomicCAS(&g_dev_status[0], 0u, 1u) == 0u) g_dev_status[1] = detail;
 }
+// true once any wait of a kernel of this translation unit has given up (and the host has not cleared it)
+__device__ __forceinline__ bool status_is_set() {
+  return *reinterpret_cast<volatile unsigned int*>(&g_dev_status[0]) != 0u;
+}
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);

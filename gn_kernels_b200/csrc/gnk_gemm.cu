@@ -20,6 +20,8 @@
 // the barriers of both CTAs.  No TMA load here uses cluster multicast.
 // Every barrier wait is bounded; a wait that runs out sets the device status word and the
 // role leaves its loop, after which the CTA tears down normally.
+#include <atomic>
+
 #include "gnk_gemm_kernel.cuh"
 
 namespace gnk {
@@ -27,8 +29,8 @@ namespace {
 
 using namespace gnk::gemm;
 
-long long* g_trace = nullptr;  // test hook (gnk_debug_trace): device buffer of 2*2*256*3 int64
-int g_max_clusters = 0;  // test hook (gnk_debug_max_clusters): cap on the persistent grid, 0 = none
+std::atomic<long long*> g_trace{nullptr};  // test hook (gnk_debug_trace): device buffer of 2*2*256*3 int64
+std::atomic<int> g_max_clusters{0};  // test hook (gnk_debug_max_clusters): cap on the persistent grid, 0 = none
 
 template <MmaKind KIND>
 struct ElemInfo {
@@ -104,7 +106,8 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
     resident[dev] = n;
   }
   int clusters = resident[dev];
-  if (g_max_clusters > 0 && clusters > g_max_clusters) clusters = g_max_clusters;
+  const int cap = g_max_clusters.load();
+  if (cap > 0 && clusters > cap) clusters = cap;
   if (clusters > tiles) clusters = tiles;
   EpiMaps<EPI> maps;
   if (C::kBulkC && g.vec_ok) {
@@ -120,12 +123,12 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
 
 // Tile choice: the largest tile that still gives every SM work; 2-CTA 256x256 for big problems.
 enum TileSel { T_2x256, T_1x256, T_1x128, T_1x64 };
-int g_force_tile = -1;  // test hook (gnk_debug_force_tile)
-int g_staged = -1;      // test hook (gnk_debug_staged)
-int g_dbg = 0;          // test hook (gnk_debug_flags)
+std::atomic<int> g_force_tile{-1};  // test hook (gnk_debug_force_tile)
+std::atomic<int> g_staged{-1};      // test hook (gnk_debug_staged)
 
 TileSel pick_tile(int64_t M, int64_t N, bool block_scaled) {
-  if (g_force_tile >= 0) return static_cast<TileSel>(g_force_tile);
+  const int forced = g_force_tile.load();
+  if (forced >= 0) return static_cast<TileSel>(forced);
   const int sms = num_sms();
   auto ctas = [&](int64_t bm, int64_t bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
   if (ctas(256, 256) * 2 >= sms) return T_2x256;
@@ -141,7 +144,7 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
   switch (pick_tile(M, N, kBS)) {
     case T_2x256:
       // g_staged: 0 = direct stores from registers, anything else = bulk tensor stores through staging
-      if (g_staged == 0) return launch<KIND, 256, 2, EPI, 0>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+      if (g_staged.load() == 0) return launch<KIND, 256, 2, EPI, 0>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
       return launch<KIND, 256, 2, EPI, 2>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x256: return launch<KIND, 256, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x128: return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
@@ -168,8 +171,7 @@ GemmArgs base_args(void* C, int64_t ldc, int64_t M, int64_t N, int out_elem_byte
   g.ldc = ldc;
   g.alpha = 1.f;
   g.vec_ok = aligned16(C) && ((ldc * out_elem_bytes) % 16 == 0);
-  g.trace = g_trace;
-  g.dbg = g_dbg;
+  g.trace = g_trace.load();
   return g;
 }
 
@@ -196,12 +198,6 @@ extern "C" int gnk_debug_trace(void* device_buffer) {
 // Debug: staged epilogue of the 256x256 pair tile: -1 = default per kind, 0 = direct stores, 1 = staged.
 extern "C" int gnk_debug_staged(int mode) {
   g_staged = mode;
-  return GNK_OK;
-}
-
-// Debug bits for timing experiments (bit 0: skip scale-factor copies; results are then wrong).
-extern "C" int gnk_debug_flags(int bits) {
-  g_dbg = bits;
   return GNK_OK;
 }
 

@@ -33,7 +33,6 @@ struct GemmArgs {
   long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
   int a_rows;        // rows of A one stage load brings in (the tensor map's box; 128 unless M < 128)
   int stages;        // pipeline depth (the launcher's choice: fewer A rows per stage leave room for more stages)
-  int dbg;           // debug bits (timing experiments only, wrong results): 1 skip scale-factor copies, 2 reduce-scatter reducers only wait, 4 reduce-scatter stores stay local
   // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
   // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
   // THIS GPU.  Flag words: one per owned 128 x BN unit, then a CTA ticket, then the exit counter.
@@ -528,7 +527,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
           const uint64_t sfb_desc = sdesc_sf(stage_sfb(stage));
           const uint32_t empty = bar_empty(stage);
           if (leader) {
-            if (kBS && !(g.dbg & 1)) {
+            if constexpr (kBS) {
               constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per stage: 1 (mxfp8) or 4 (nvfp4)
 #pragma unroll
               for (int a = 0; a < kAtoms; ++a) {
@@ -609,11 +608,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         // this rank's slot in the staging buffer of the rank that owns the row
         const int owner = row / g.rs.rows_per_owner;
         const int lrow = row - owner * g.rs.rows_per_owner;
-        // (debug bit 4: keep the stores on this GPU - timing experiments only, wrong results)
         if (g.rs.mc_partial)  // pull variant: the row's place in this rank's own [M, N] partial
           rowptr = g.rs.staging[g.rs.rank] + static_cast<int64_t>(row) * g.N;
         else
-          rowptr = g.rs.staging[(g.dbg & 4) ? g.rs.rank : owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
+          rowptr = g.rs.staging[owner] + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + lrow) * g.N;
         const int lrow0 = (tm * CG + cta_rank) * 128 - owner * g.rs.rows_per_owner;
         rs_flag = g.rs.flags[owner] + (lrow0 / 128) * g.tiles_n + tn;
       } else if constexpr (EPI == EPI_I32) {
@@ -694,14 +692,13 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         if (lane == 0) {
           const int row0 = (tm * CG + cta_rank) * 128 + warp * 32;
           const int owner = row0 / g.rs.rows_per_owner;
-          const int dst = (g.dbg & 4) ? g.rs.rank : owner;
           if (g.rs.mc_partial) {
 #pragma unroll
             for (int cb = 0; cb < BN / 64; ++cb) tma_store_2d(&epi_maps.local, stg + cb * 4096, ncol0 + cb * 64, row0);
           } else {
 #pragma unroll
             for (int cb = 0; cb < BN / 64; ++cb)
-              tma_store_2d(&epi_maps.slot[dst], stg + cb * 4096, ncol0 + cb * 64, row0 - owner * g.rs.rows_per_owner);
+              tma_store_2d(&epi_maps.slot[owner], stg + cb * 4096, ncol0 + cb * 64, row0 - owner * g.rs.rows_per_owner);
           }
           tma_store_commit();
           pending_flag = rs_flag;
@@ -761,6 +758,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       const int items = units * parts;
       unsigned int* done = my_flags + units;  // items finished per unit
       unsigned long long red_wait = 0;
+      bool rs_dead = false;  // thread ct == 0 only: a flag wait of this CTA has run out
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int q = item / (CG * parts), rem = item - q * (CG * parts);
         int lm, tn;
@@ -770,12 +768,19 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         const int c0 = tn * BN;
         if (ct == 0) {
           const unsigned long long w0 = rs_tr ? globaltimer_ns() : 0;
-          // every rank's four epilogue warps signal their 32-row pieces of the unit separately
-          rs_ok = wait_flag_eq(my_flags + u, 4u * g.rs.world, g.rs.timeout_ms, (4u << 24) | (6u << 16) | (u & 0xFFFF));
+          // every rank's four epilogue warps signal their 32-row pieces of the unit separately.
+          // Giving up is paid once: after the first wait of this CTA (or of any CTA, through the
+          // sticky status word) has run out, the remaining items are skipped without polling.
+          if (rs_dead || status_is_set()) {
+            rs_ok = 0;
+          } else {
+            rs_ok = wait_flag_eq(my_flags + u, 4u * g.rs.world, g.rs.timeout_ms, (4u << 24) | (6u << 16) | (u & 0xFFFF));
+            if (!rs_ok) rs_dead = true;
+          }
           if (rs_tr) red_wait += globaltimer_ns() - w0;
         }
         asm volatile("bar.sync 3, 128;" ::: "memory");
-        if (rs_ok && !(g.dbg & 2)) {  // (debug bit 2: wait and reset only - timing experiments)
+        if (rs_ok) {
           for (int c = 0; c < span; ++c) {
             const int lr0 = rb * 128 + ((rem % parts) * span + c) * chunk_rows;
             if (pull) reduce_chunk_multimem<BN, 8>(g, lr0, c0, ct, stream_pol);
@@ -819,7 +824,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         __threadfence_system();
         for (int p = 0; p < g.rs.world; ++p)
           if (p != g.rs.rank) red_release_sys_add(g.rs.flags[p] + 2 * units + 1, 1u);
-        if (wait_flag_eq(my_flags + 2 * units + 1, g.rs.world - 1, g.rs.timeout_ms, (4u << 24) | (7u << 16)))
+        // a call that has already given up somewhere does not wait a second time: the flag words are
+        // then left as they are and the caller re-zeroes them (see gnk_gemm_rs_bf16 in gnk.h)
+        if (!status_is_set() &&
+            wait_flag_eq(my_flags + 2 * units + 1, g.rs.world - 1, g.rs.timeout_ms, (4u << 24) | (7u << 16)))
           my_flags[2 * units + 1] = 0u;
       }
     }

@@ -20,8 +20,7 @@
 // multimem.ld_reduce (NVSwitch fetches it from every rank and adds in fp32), so an SM receives
 // only the reduced data: world times less than the push variant's slot reads, which compete
 // with the main loop's operand loads for the SM's L2 port.
-#include <cstdio>
-#include <cstdlib>
+#include <atomic>
 
 #include "gnk_gemm_kernel.cuh"
 
@@ -32,14 +31,8 @@ using namespace gnk::gemm;
 
 GNK_DEFINE_STATUS_READER(gemm_rs_status_reader)
 
-// timing experiments: GNK_RS_DEBUG=<bits> in the environment (read once)
-int rs_debug_bits() {
-  static int bits = [] {
-    const char* e = getenv("GNK_RS_DEBUG");
-    return e ? atoi(e) : 0;
-  }();
-  return bits;
-}
+// test hook (gnk_debug_rs_trace): caller-owned device buffer receiving 8 globaltimer words per CTA
+std::atomic<unsigned long long*> g_rs_trace{nullptr};
 
 struct RsPlan {
   int cg, bn;
@@ -121,37 +114,9 @@ int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g
   rc = make_tmap_2d(&maps.local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.rs.staging[g.rs.rank], M, N, N * 2, 32, 64,
                     CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
-  // timing experiments: GNK_RS_TRACE=1 prints a per-call timeline summary (synchronises the stream)
-  static const bool trace_on = getenv("GNK_RS_TRACE") != nullptr;
-  static unsigned long long* trace_dev[64];
-  if (trace_on) {
-    if (!trace_dev[dev]) GNK_CUDA_OK(cudaMalloc(&trace_dev[dev], 8 * sizeof(unsigned long long) * 1024));
-    GNK_CUDA_OK(cudaMemsetAsync(trace_dev[dev], 0, 8 * sizeof(unsigned long long) * 1024, st));
-    g.rs.trace = trace_dev[dev];
-  }
+  g.rs.trace = g_rs_trace.load();
   kern<<<clusters * CG, 320, C::kSmemBytes, st>>>(tm_a, tm_b, tm_a, tm_b, maps, g);
   GNK_LAUNCH_OK();
-  if (trace_on) {
-    static unsigned long long h[8 * 1024];
-    GNK_CUDA_OK(cudaStreamSynchronize(st));
-    GNK_CUDA_OK(cudaMemcpy(h, trace_dev[dev], sizeof(h), cudaMemcpyDeviceToHost));
-    const int n = clusters * CG;
-    unsigned long long t0 = ~0ull;
-    for (int b = 0; b < n; ++b)
-      if (h[b * 8] && h[b * 8] < t0) t0 = h[b * 8];
-    double mx[8] = {0}, sum[8] = {0};
-    for (int b = 0; b < n; ++b)
-      for (int k = 0; k < 8; ++k) {
-        const double v = (k == 3 || k == 5 || k == 6) ? h[b * 8 + k] * 1e-3 : (h[b * 8 + k] ? (h[b * 8 + k] - t0) * 1e-3 : 0.0);
-        sum[k] += v;
-        if (v > mx[k]) mx[k] = v;
-      }
-    fprintf(stderr,
-            "RS_TRACE rank %d us: start max %.1f | mma end mean %.1f max %.1f | epi end mean %.1f max %.1f | red end mean "
-            "%.1f max %.1f | red wait mean %.1f | epi store+signal mean %.1f | epi wait-acc mean %.1f\n",
-            g.rs.rank, mx[0], sum[4] / (n / CG), mx[4], sum[1] / n, mx[1], sum[2] / n, mx[2], sum[3] / n, sum[5] / n,
-            sum[6] / n);
-  }
   return GNK_OK;
 }
 
@@ -159,6 +124,14 @@ int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g
 }  // namespace gnk
 
 using namespace gnk;
+
+// Debug: per-CTA timeline of the next reduce-scatter calls.  `device_buffer` (caller-owned, zeroed by the
+// caller, 8 uint64 per CTA, room for 160 CTAs) receives globaltimer stamps: start, epilogue end,
+// reducer end, reducer wait total, MMA end, epilogue store+signal total, epilogue wait total.  NULL = off.
+extern "C" int gnk_debug_rs_trace(void* device_buffer) {
+  g_rs_trace = static_cast<unsigned long long*>(device_buffer);
+  return GNK_OK;
+}
 
 extern "C" int64_t gnk_gemm_rs_flag_words(int64_t M, int64_t N, int world) {
   RsPlan p;
@@ -222,7 +195,6 @@ int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c
     g.rs.staging[r] = static_cast<__nv_bfloat16*>(staging[r]);
     g.rs.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
   }
-  g.dbg = rs_debug_bits();
   g.rs.mc_partial = static_cast<const __nv_bfloat16*>(multicast);
   g.rs.out = static_cast<__nv_bfloat16*>(output);
   g.rs.ldo = ldo;

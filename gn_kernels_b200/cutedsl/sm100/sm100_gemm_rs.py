@@ -22,6 +22,34 @@ def flag_words(M: int, N: int, world_size: int) -> int:
     return int(n)
 
 
+def peer_addresses(t: torch.Tensor, handle, rank: int, world: int, need_bytes: int, align: int = 16) -> tuple[list[int], int]:
+    """Addresses of `t` (a contiguous tensor inside this rank's symmetric allocation) as mapped for
+    every rank, and its multicast address (0 if the handle has none).
+
+    `handle.buffer_ptrs` are allocation bases; `t` may be a view or a sub-allocation, so ONE byte
+    offset (t.data_ptr() minus this rank's base) is applied to every peer base and to the multicast
+    base alike.  Using the bases for some and an offset address for others would make ranks write
+    to one place and read from another."""
+    if not t.is_contiguous():
+        raise ValueError("gemm_rs: symmetric buffers must be contiguous")
+    bases = [int(p) for p in handle.buffer_ptrs[:world]]
+    if len(bases) != world:
+        raise ValueError(f"gemm_rs: the symmetric-memory handle maps {len(bases)} ranks, need {world}")
+    off = int(t.data_ptr()) - bases[rank]
+    size = int(getattr(handle, "buffer_size", 0) or 0)
+    if off < 0 or (size and off + need_bytes > size):
+        raise ValueError(f"gemm_rs: tensor does not lie inside the symmetric allocation (offset {off}, need {need_bytes}, allocation {size})")
+    if t.numel() * t.element_size() < need_bytes:
+        raise ValueError(f"gemm_rs: symmetric buffer too small ({t.numel() * t.element_size()} bytes, need {need_bytes})")
+    if off % align:
+        raise ValueError(f"gemm_rs: symmetric buffer must start {align}-byte aligned inside the allocation")
+    try:
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+    except Exception:
+        mc = 0
+    return [b + off for b in bases], (mc + off if mc else 0)
+
+
 def gemm_rs(
     x: torch.Tensor,
     w: torch.Tensor,
@@ -55,24 +83,20 @@ def gemm_rs(
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and output.dtype == torch.bfloat16
     assert w.shape[1] == K and output.shape == (M // world, N)
     assert x.stride(1) == 1 and w.stride(1) == 1 and output.stride(1) == 1
-    if world > 1:
-        assert partial.numel() >= M * N and partial.dtype == torch.bfloat16
-        assert flags.dtype == torch.int32 and flags.numel() >= flag_words(M, N, world)
-        sp = (ctypes.c_void_p * world)(*[int(p) for p in partial_handle.buffer_ptrs[:world]])
-        fp = (ctypes.c_void_p * world)(*[int(p) for p in flags_handle.buffer_ptrs[:world]])
-    else:
-        sp = fp = None
     stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
     mc = 0
-    if world > 1 and multicast is not False:
-        try:
-            mc = int(getattr(partial_handle, "multicast_ptr", 0) or 0)
-        except Exception:
-            mc = 0
-        if mc == 0 and multicast:
-            raise RuntimeError("gemm_rs: multicast=True but the symmetric-memory handle has no multicast address")
+    sp = fp = None
+    if world > 1:
+        assert partial.dtype == torch.bfloat16 and flags.dtype == torch.int32
+        p_addr, p_mc = peer_addresses(partial, partial_handle, rank, world, M * N * 2)
+        f_addr, _ = peer_addresses(flags, flags_handle, rank, world, flag_words(M, N, world) * 4, align=4)
+        sp = (ctypes.c_void_p * world)(*p_addr)
+        fp = (ctypes.c_void_p * world)(*f_addr)
+        if multicast is not False:
+            mc = p_mc
+            if mc == 0 and multicast:
+                raise RuntimeError("gemm_rs: multicast=True but the symmetric-memory handle has no multicast address")
     if mc:
-        mc += partial.storage_offset() * partial.element_size()
         with torch.cuda.device(x.device):
             check(
                 lib().gnk_gemm_rs_bf16_pull(

@@ -2,8 +2,10 @@
  * gnk.h - C ABI of libgnk.so: hand-written sm_100a kernels behind the gn_kernels Python API.
  *
  * Every entry point takes plain device pointers and sizes, launches on the given CUDA
- * stream, allocates nothing, never throws and never exits; it returns GNK_OK (0) or a
- * negative GNK_ERR_* code (gnk_strerror gives the text).  Outputs are caller-allocated.
+ * stream, allocates no device memory, never throws and never exits; it returns GNK_OK (0)
+ * or a negative GNK_ERR_* code (gnk_strerror gives the text).  Outputs are caller-allocated.
+ * Entry points may be called from several host threads; encoded TMA descriptors are kept in a
+ * small mutex-guarded host cache.  Only the gnk_debug_* hooks at the end are process-wide.
  * Kernels whose warps wait on hardware barriers bound every wait; a wait that runs out
  * is recorded in a sticky device status word readable with gnk_device_status().
  *
@@ -142,7 +144,8 @@ int gnk_mm_f8(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, 
               const float* bias, gnk_stream_t stream);
 
 /* MXFP8: C bf16 = (A .* 2^(SFA-127)) * (Bt .* 2^(SFB-127))^T.  A, Bt E4M3; SFA, SFB E8M0
- * in the swizzled 128x4-atom layout ([ceil128(rows), K/32] bytes).  K % 128 == 0.
+ * in the swizzled 128x4-atom layout ([ceil128(rows), ceil4(K/32)] bytes).  K % 32 == 0 (a K that is
+ * not a multiple of 128 ends in a partly filled stage: TMA reads zeros beyond K).
  * Replaces: gn_kernels/cutedsl/sm100/sm100_mm_mxfp8.py:380-383 `mm`. */
 int gnk_mm_mxfp8(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA,
                  const uint8_t* SFB, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
@@ -150,7 +153,7 @@ int gnk_mm_mxfp8(const void* A, int64_t lda, const void* Bt, int64_t ldb, const 
 
 /* NVFP4: A, Bt packed E2M1 ([rows, K/2] bytes, ld in bytes), SFA/SFB E4M3 per 16, swizzled
  * ([ceil128(rows), K/16] bytes); alpha (host value, = tensor_scale_A * tensor_scale_B)
- * multiplies the fp32 accumulator before the bf16 rounding.  K % 256 == 0.
+ * multiplies the fp32 accumulator before the bf16 rounding.  K % 32 == 0 (16-byte rows of packed codes).
  * Replaces: gn_kernels/cutedsl/sm100/sm100_mm_nvfp4.py:383-386 `mm` (upstream has no
  * alpha; gn_kernels/cutedsl/sm120/sm120_gated_gemm_nvfp4.py:317-319 shows where it goes). */
 int gnk_mm_nvfp4(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA,
@@ -193,13 +196,21 @@ int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, int64_t i, i
 /* K-sharded bf16 GEMM fused with a reduce-scatter along M over NVLink peer memory.
  * x [M, K_local], w [N, K_local] (this rank's K shard).  staging[r] / flags[r]: device
  * pointers, valid on THIS GPU, to rank r's staging buffer (M * N bf16: `world` slots of
- * [M/world, N]) and flag words (zero before the first call; the kernel leaves them zero).
+ * [M/world, N]) and flag words (zero before the first call; a call that completes leaves them zero).
  * Every rank stores each finished bf16 tile into the owner's staging slot for this rank and
  * bumps the owner's flag; the owner sums the `world` slots from its own memory in fp32 and
- * writes output [M/world, N] bf16; an exit barrier across ranks ends the call.  All
- * device-side waits are bounded by timeout_ms (0 = 20 s; GNK_ERR_TIMEOUT through
- * gnk_device_status).  M % (128*world) == 0, N % 128 == 0, K_local % 8 == 0, world <= 8.
- * world == 1 degenerates to gnk_mm_bf16 into `output`.
+ * writes output [M/world, N] bf16; an exit barrier across ranks ends the call.
+ * Shapes: M % (128*world) == 0 and N % 128 == 0, K_local % 8 == 0, world <= 8.  When M/world % 256 == 0 and
+ * N % 256 == 0 the 2-CTA 256 x 256 tile with bulk-store epilogue runs, otherwise a 128 x 128 tile with
+ * plain peer stores.  world == 1 degenerates to gnk_mm_bf16 into `output`.
+ * Failure: all device-side waits are bounded by timeout_ms (0 = 20 s).  When a peer never signals, the
+ * first wait of a CTA that runs out records GNK_ERR_TIMEOUT (gnk_device_status; detail = role 4,
+ * barrier 6 = unit flag, 7 = exit barrier) and every later wait of the call returns at once, so a
+ * call costs at most about 2 x timeout_ms; the rows it could not reduce are left unwritten.  After
+ * GNK_ERR_TIMEOUT the flag words are NOT zero: before the buffers are used again every rank must
+ * finish or abandon its call, clear the status (gnk_device_status(..., clear = 1)), zero its flags
+ * buffer, and meet the other ranks in a host barrier.  While the status word is set, further calls
+ * skip their reductions.
  * Replaces: gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496 `gemm_rs`. */
 int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
                      int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
@@ -217,15 +228,19 @@ int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw
                           gnk_stream_t stream);
 
 /* ------------------------------------------------------------------ test hooks ---- */
-/* Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, -1: automatic),
- * cap the persistent grid (0 = no cap), record per-stage clock stamps of CTAs 0 and 1 into a device
- * buffer of 2*2*256*3 int64 (NULL = off).  Process-wide; for tests and profiling only. */
+/* Process-wide switches for tests and profiling; none of them changes a result.
+ * Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, -1: automatic),
+ * cap the persistent grid (0 = no cap), record per-stage clock stamps of CTAs 0 and 1 into a
+ * caller-owned device buffer of 2*2*256*3 int64 (NULL = off). */
 int gnk_debug_force_tile(int sel);
 int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default (staged), 0 direct stores from registers, 1 bulk tensor stores through shared-memory staging */
 int gnk_debug_max_clusters(int n);
-int gnk_debug_flags(int bits); /* timing experiments only: bit 0 skips scale-factor copies (wrong results) */
 int gnk_debug_trace(void* device_buffer);
 int gnk_debug_attn_trace(void* device_buffer); /* attention: clock stamps of CTA 0, 2 tiles x 32 key tiles x 8 int64 (NULL = off) */
+/* GEMM + reduce-scatter: per-CTA timeline into a caller-owned, caller-zeroed device buffer of 160 x 8
+ * uint64 (globaltimer ns: start, epilogue end, reducer end, reducer wait total, MMA end, epilogue
+ * store+signal total, epilogue wait total); NULL = off. */
+int gnk_debug_rs_trace(void* device_buffer);
 
 #ifdef __cplusplus
 }

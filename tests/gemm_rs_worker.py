@@ -1,10 +1,12 @@
 """Multi-GPU worker for the GEMM + reduce-scatter parity test and benchmark.
 
-    torchrun --nnodes=1 --nproc-per-node=W --master-addr 127.0.0.1 --master-port P tests/gemm_rs_worker.py [--bench]
+    torchrun --nnodes=1 --nproc-per-node=W --master-addr 127.0.0.1 --master-port P tests/gemm_rs_worker.py [--multicast 0|1] [--trace]
 
-Each rank holds its K shard; outputs are gathered on rank 0 and compared with the CPU oracle."""
+Each rank holds its K shard; outputs are gathered on rank 0 and compared with the CPU oracle.
+Timing lives in bench.py (--workload bf16_gemm_rs under torchrun)."""
 
 import argparse
+import ctypes
 import os
 import sys
 
@@ -18,8 +20,9 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--bench", action="store_true")
-    ap.add_argument("--k-total", type=int, default=28672, help="bench: K summed over ranks")
+    ap.add_argument("--trace", action="store_true", help="print a per-role timeline of one full-size call instead of the parity cases")
+    ap.add_argument("--k-total", type=int, default=28672, help="--trace: K summed over ranks")
+    ap.add_argument("--timeout-ms", type=int, default=5000, help="bound of the device-side waits")
     ap.add_argument("--symm-backend", default="", help="torch symmetric-memory backend (empty = torch's default)")
     ap.add_argument("--multicast", type=int, default=-1, help="-1 automatic, 0 push over peer stores, 1 pull through the multicast address")
     args = ap.parse_args()
@@ -35,10 +38,12 @@ def main():
     if args.symm_backend:  # torch's default backend offers a multicast address on NVSwitch systems
         symm_mem.set_backend(args.symm_backend)
     rank, W = dist.get_rank(), dist.get_world_size()
+    if rank == 0:  # the launcher pins every rank to one host thread; rank 0 runs the CPU oracle
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     mcast = None if args.multicast < 0 else bool(args.multicast)
 
     def gemm_rs(*a, **k):  # every call below goes through the chosen data path
-        return _gemm_rs(*a, multicast=mcast, **k)
+        return _gemm_rs(*a, multicast=mcast, timeout_ms=args.timeout_ms, **k)
 
     def alloc(M, N):
         partial = symm_mem.empty(M, N, dtype=torch.bfloat16, device=dev)
@@ -54,7 +59,8 @@ def main():
         return partial, ph, flags, fh
 
     failures = 0
-    cases = [(256 * W, 256, 512), (512 * W, 768, 1024), (128 * W, 384, 320)] if not args.bench else []
+    # the last case has the benchmark's M and N (every CTA reduces several units) with a short K
+    cases = [(256 * W, 256, 512), (512 * W, 768, 1024), (128 * W, 384, 320), (8192, 8192, 256)] if not args.trace else []
     for M, N, Kt in cases:
         Kl = Kt
         g = torch.Generator().manual_seed(1234 + rank)
@@ -62,19 +68,19 @@ def main():
         w = (torch.randn(N, Kl, generator=g) / (Kl * W) ** 0.5).bfloat16().to(dev)
         partial, ph, flags, fh = alloc(M, N)
         out = torch.empty(M // W, N, dtype=torch.bfloat16, device=dev)
+        xs = [torch.empty_like(x) for _ in range(W)]
+        ws = [torch.empty_like(w) for _ in range(W)]
+        dist.all_gather(xs, x)
+        dist.all_gather(ws, w)
+        refs = ors.gemm_rs([t.cpu() for t in xs], [t.cpu() for t in ws]) if rank == 0 else None
         for it in range(3):  # repeated calls reuse flags and staging (exit barrier + flag reset)
             out.zero_()
             gemm_rs(x, w, partial, ph, out, flags, fh)
             torch.cuda.synchronize()
             _lib.raise_on_device_error()
-            xs = [torch.empty_like(x) for _ in range(W)]
-            ws = [torch.empty_like(w) for _ in range(W)]
             outs = [torch.empty_like(out) for _ in range(W)]
-            dist.all_gather(xs, x)
-            dist.all_gather(ws, w)
             dist.all_gather(outs, out)
             if rank == 0:
-                refs = ors.gemm_rs([t.cpu() for t in xs], [t.cpu() for t in ws])
                 errs = [max_rel_err(o.cpu(), r) for o, r in zip(outs, refs)]
                 exact = all(torch.equal(o.cpu(), r) for o, r in zip(outs, refs))
                 ok = max(errs) <= 1e-2
@@ -84,52 +90,38 @@ def main():
             dist.barrier()  # a faster peer's next call may signal this rank's flags as soon as it starts
         dist.barrier()
 
-    if args.bench:
+    if args.trace:
+        # per-role timeline of one full-size call (M = N = 8192): the kernel writes globaltimer stamps per CTA
+        # into a caller-owned buffer (gnk_debug_rs_trace); rank 0 prints a summary in microseconds
         M = N = 8192
-        Kt = args.k_total
-        Kl = Kt // W
+        Kl = args.k_total // W
         g = torch.Generator().manual_seed(1234 + rank)
-        x = (torch.randn(M, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)
-        w = (torch.randn(N, Kl, generator=g) / Kt**0.5).bfloat16().to(dev)
+        x = (torch.randn(M, Kl, generator=g) / args.k_total**0.5).bfloat16().to(dev)
+        w = (torch.randn(N, Kl, generator=g) / args.k_total**0.5).bfloat16().to(dev)
         out = torch.empty(M // W, N, dtype=torch.bfloat16, device=dev)
-        if W > 1:
-            partial, ph, flags, fh = alloc(M, N)
-        else:
-            partial = ph = flags = fh = None
-        for _ in range(5):
+        partial, ph, flags, fh = alloc(M, N)
+        for _ in range(3):
             gemm_rs(x, w, partial, ph, out, flags, fh)
         torch.cuda.synchronize()
         dist.barrier()
-        steps = 20
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            gemm_rs(x, w, partial, ph, out, flags, fh)
-        e1.record()
+        buf = torch.zeros(160 * 8, dtype=torch.int64, device=dev)
+        L = _lib.lib()
+        L.gnk_debug_rs_trace(ctypes.c_void_p(buf.data_ptr()))
+        gemm_rs(x, w, partial, ph, out, flags, fh)
         torch.cuda.synchronize()
+        L.gnk_debug_rs_trace(None)
         _lib.raise_on_device_error()
-        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        # plain GEMM of the same local shape for the compute-only reference point
-        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-        from gn_kernels_b200 import ops
-
-        for _ in range(3):
-            ops.mm_bf16(x, w)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(steps):
-            ops.mm_bf16(x, w)
-        e1.record()
-        torch.cuda.synchronize()
-        tg = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
-        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
-        if rank == 0:
-            fl = 2.0 * M * N * Kt
-            print(f"GEMM_RS_BENCH W={W} M={M} N={N} K={Kt}: {float(t):.3f} ms/step, {fl / float(t) / 1e9:.0f} TFLOP/s total; "
-                  f"local GEMM alone {float(tg):.3f} ms ({fl / float(tg) / 1e9:.0f} TFLOP/s total)", flush=True)
+        h = buf.cpu().view(160, 8)
+        h = h[h[:, 0] > 0]
+        t0 = int(h[:, 0].min())
+        us = lambda col: (h[:, col][h[:, col] > 0] - t0).double() * 1e-3  # noqa: E731
+        tot = lambda col: h[:, col].double() * 1e-3  # noqa: E731
+        print(f"RS_TRACE rank {rank} W={W} K={args.k_total} CTAs {h.shape[0]} us: start max {us(0).max():.1f} | mma end mean {us(4).mean():.1f} max {us(4).max():.1f} | "
+              f"epi end mean {us(1).mean():.1f} max {us(1).max():.1f} | red end mean {us(2).mean():.1f} max {us(2).max():.1f} | red wait mean {tot(3).mean():.1f} | "
+              f"epi store+signal mean {tot(5).mean():.1f} | epi wait-acc mean {tot(6).mean():.1f}", flush=True)
+        dist.barrier()
     dist.barrier()
-    if rank == 0 and not args.bench:
+    if rank == 0 and not args.trace:
         print("GEMM_RS_OK" if failures == 0 else "GEMM_RS_FAILED", flush=True)
     dist.destroy_process_group()
     sys.exit(1 if failures else 0)

@@ -93,3 +93,37 @@ def test_sharding_semantics_two_gloo_ranks():
     for p in procs:
         p.join(timeout=60)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+class _FakeHandle:
+    """Stand-in for a torch symmetric-memory handle: allocation bases per rank and a multicast base."""
+
+    def __init__(self, bases, size, mc=0):
+        self.buffer_ptrs, self.buffer_size, self.multicast_ptr = bases, size, mc
+
+
+def test_peer_addresses_apply_one_offset_to_every_mapping():
+    from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import peer_addresses
+
+    pool = torch.zeros(1 << 16, dtype=torch.uint8)
+    base = pool.data_ptr()
+    bases = [0x7000_0000_0000, base, 0x7200_0000_0000]  # this rank (1) maps its own allocation at `base`
+    h = _FakeHandle(bases, pool.numel(), mc=0x7F00_0000_0000)
+    view = pool[4096 : 4096 + 8192].view(torch.bfloat16).view(64, 64)  # a sub-allocation 4096 bytes in
+    peers, mc = peer_addresses(view, h, rank=1, world=3, need_bytes=8192)
+    assert peers == [b + 4096 for b in bases] and mc == 0x7F00_0000_0000 + 4096
+    whole = pool.view(torch.bfloat16)
+    peers, mc = peer_addresses(whole, h, rank=1, world=3, need_bytes=1024)
+    assert peers == bases and mc == 0x7F00_0000_0000
+    # no multicast mapping: address 0 selects the peer-store path
+    assert peer_addresses(whole, _FakeHandle(bases, pool.numel()), 1, 3, 1024)[1] == 0
+    with pytest.raises(ValueError):  # a strided view cannot be addressed as one block
+        peer_addresses(pool.view(torch.bfloat16).view(128, 256)[:, :64], h, 1, 3, 64)
+    with pytest.raises(ValueError):  # runs past the end of the allocation
+        peer_addresses(pool[65000:].view(torch.bfloat16), h, 1, 3, 4096)
+    with pytest.raises(ValueError):  # too small for the problem
+        peer_addresses(view, h, 1, 3, 8192 + 2)
+    with pytest.raises(ValueError):  # misaligned start
+        peer_addresses(pool[8 : 8 + 4096].view(torch.bfloat16), h, 1, 3, 4096)
+    flags = pool[4 : 4 + 64].view(torch.int32)
+    assert peer_addresses(flags, h, 1, 3, 64, align=4)[0][1] == base + 4

@@ -1,20 +1,27 @@
 """GPU parity: tcgen05 attention forward (8-bit QK + scales, bf16 V) vs the CPU oracle.
 
-Bound: max|out-ref| / max|ref| <= 1e-2 against the fp32 dequantise-then-softmax oracle, plus
-the upstream test's own elementwise tolerance (rtol 1.6e-2, atol 1e-3,
-tests/test_triton_attn.py:41) loosened only by the bf16 rounding of P that upstream's kernel
-also performs."""
+Bound, on every case: max|out-ref| / max|ref| <= 1e-2 against the fp32 dequantise-then-softmax
+oracle, and element-wise the upstream test's tolerance (rtol 1.6e-2, tests/test_triton_attn.py:41)
+with atol 4e-3 instead of 1e-3: the oracle keeps P in fp32 while the kernel (like upstream's)
+rounds P to bf16 before P*V."""
 
 import numpy as np
 import pytest
 import torch
 
 from conftest import bf16_from_bits
-from gpu_util import SEED_ATTN, rel_err, u8
+from gpu_util import SEED_ATTN, assert_parity, rel_err, u8
 from oracle import attn as oattn
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
+
+
+def assert_attn(out, ref):
+    """Global max|out-ref| <= 1e-2 * max|ref|, and element-wise upstream's rtol 1.6e-2 with atol 4e-3
+    (upstream's 1e-3 is for a comparison in which both sides round P to bf16; the fp32 oracle here
+    does not round P, which costs up to 2^-9 of a row's largest probability times |V|)."""
+    assert_parity(out, ref, tol=TOL, elem_rtol=1.6e-2, atol_abs=4e-3)
 
 
 @pytest.fixture(scope="module")
@@ -50,8 +57,7 @@ def test_upstream_shapes_golden_inputs(gk, golden_attn, dt, shape, causal):
     q, k, v = (bf16_from_bits(g[f"{shape}_{n}"]).cuda() for n in "qkv")
     out, ref = run_case(gk, q, k, v, dt, causal)
     assert out.shape == ref.shape and out.dtype == torch.bfloat16
-    assert rel_err(out, ref) <= TOL
-    torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=1.6e-2, atol=4e-3)
+    assert_attn(out, ref)
     # against the upstream test oracle on the UNquantised inputs: quantisation noise only
     sdpa = bf16_from_bits(g[f"{shape}_o_{int(causal)}"])
     assert rel_err(out, sdpa) <= 0.1
@@ -66,7 +72,7 @@ def test_shapes(gk, dt, B, Lq, Lk, Hq, Hkv, causal):
     k = torch.randn(B, Lk, Hkv, 128, generator=g).bfloat16().cuda()
     v = torch.randn(B, Lk, Hkv, 128, generator=g).bfloat16().cuda()
     out, ref = run_case(gk, q, k, v, dt, causal)
-    assert rel_err(out, ref) <= TOL
+    assert_attn(out, ref)
     if causal and Lq > Lk:  # rows that see no key are zero (upstream triton_attn.py:236-237)
         assert not out[:, : Lq - Lk].float().abs().any()
 
@@ -80,7 +86,7 @@ def test_peaked_scores_exercise_rescale(gk):
     v = torch.randn(1, 1024, 2, 128, generator=g).bfloat16().cuda()
     for causal in (False, True):
         out, ref = run_case(gk, q, k, v, torch.float8_e4m3fn, causal)
-        assert rel_err(out, ref) <= TOL
+        assert_attn(out, ref)
 
 
 def test_unscaled_and_strided(gk):
@@ -91,7 +97,7 @@ def test_unscaled_and_strided(gk):
     v = vbig[..., :128]  # strided view: last dim contiguous, other strides arbitrary (upstream :281-286)
     out = gk.triton_attn(q, k, v, causal=True)
     ref = oattn.attention_f32(q.float().cpu(), k.float().cpu(), v.cpu(), causal=True).bfloat16()
-    assert rel_err(out, ref) <= TOL
+    assert_attn(out, ref)
 
 
 def test_benchmark_configuration_subset(gk):
@@ -112,7 +118,7 @@ def test_benchmark_configuration_subset(gk):
             hk = h // 4
             ref = oattn.attention_qk_quantized(u8(qq[b : b + 1, :, h : h + 1]), u8(kq[b : b + 1, :, hk : hk + 1]), v[b : b + 1, :, hk : hk + 1],
                                                sq[b : b + 1, h : h + 1], sk[b : b + 1, hk : hk + 1], kind="e4m3", causal=True)
-            assert rel_err(out[b : b + 1, :, h : h + 1], ref) <= TOL
+            assert_attn(out[b : b + 1, :, h : h + 1], ref)
 
 
 def test_bad_arguments(gk):
