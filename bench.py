@@ -379,7 +379,7 @@ def build_gpu_workload(name: str, dev: torch.device, timeout_ms: int = 2000) -> 
         o = torch.empty(B, Lq, Hq, D, dtype=torch.bfloat16, device=dev)
         I3 = ctypes.c_int64 * 3
         st = [I3(*t.stride()[:3]) for t in (qq, kq, v, o)]
-        step = lambda: L.gnk_attn_fwd(P(qq), P(kq), P(v), P(o), P(sq), P(sk), 1, B, Lq, Lq, Hq, Hkv, D, st[0], st[1], st[2], st[3], 1, stream())  # noqa: E731
+        step = lambda: L.gnk_attn_fwd(P(qq), P(kq), P(v), P(o), P(sq), P(sk), 1, 0, 0, B, Lq, Lq, Hq, Hkv, D, st[0], st[1], st[2], st[3], 1, stream())  # noqa: E731
         api = lambda a, b, c, d, e: gk.triton_attn(a, b, c, d, e, causal=True)  # noqa: E731
         qt, kt, vt = qf.transpose(1, 2), kf.transpose(1, 2), v.transpose(1, 2)  # [B, H, L, D] views for SDPA
         w["comparators"]["torch SDPA bf16 causal GQA (library flash attention, unquantised QK)"] = lambda: torch.nn.functional.scaled_dot_product_attention(

@@ -17,7 +17,7 @@ from .quant_utils import (
     quantize_rowwise,
     unpermute_nv_sf,
 )
-from .triton_attn import triton_attn
+from .triton_attn import triton_attn, triton_varlen_attn
 from .triton_mm import triton_mm
 
 __all__ = [
@@ -32,5 +32,6 @@ __all__ = [
     "quantize_rowwise",
     "triton_attn",
     "triton_mm",
+    "triton_varlen_attn",
     "unpermute_nv_sf",
 ]

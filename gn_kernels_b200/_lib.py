@@ -16,7 +16,7 @@ _lib = None
 
 # enums of include/gnk.h
 BF16, F16, F32 = 0, 1, 2
-Q_INT8, Q_E4M3, Q_E5M2, Q_E2M1 = 0, 1, 2, 3
+Q_INT8, Q_E4M3, Q_E5M2, Q_E2M1, Q_BF16, Q_F16 = 0, 1, 2, 3, 4, 5
 MX_OCP, MX_NV = 0, 1
 OUT_BF16, OUT_I32 = 0, 1
 
@@ -42,8 +42,10 @@ _SIGNATURES = {
     "gnk_mm_f8": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gnk_mm_mxfp8": (c_int, [_P, c_int64, _P, c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_mm_nvfp4": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_float, _P, c_int64, c_int64, c_int64, c_int64, _P]),
-    "gnk_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+    "gnk_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                              POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int, _P]),
+    "gnk_attn_varlen_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                    POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int, _P]),
     "gnk_mm_f8_block128": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, _P, c_int64, _P, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_gemm_rs_flag_words": (c_int64, [c_int64, c_int64, c_int]),
     "gnk_gemm_rs_plan": (c_int64, [c_int64, c_int64, c_int, c_int, c_int64, POINTER(c_int32)]),

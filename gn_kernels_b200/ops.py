@@ -324,27 +324,34 @@ def _blhd_ok(t: Tensor) -> bool:
     return t.stride(-1) == 1 and all((t.stride(i) * es) % 16 == 0 for i in range(3)) and t.data_ptr() % 16 == 0
 
 
+_ATTN_QK = {torch.int8: _lib.Q_INT8, torch.float8_e4m3fn: _lib.Q_E4M3, torch.bfloat16: _lib.Q_BF16, torch.float16: _lib.Q_F16}
+
+
 @torch.library.custom_op("gnk::attn_fwd", mutates_args=())
-def attn_fwd(q: Tensor, k: Tensor, v: Tensor, scale_q: Tensor | None, scale_k: Tensor | None, causal: bool) -> Tensor:
-    """q [B,Lq,Hq,D], k [B,Lk,Hkv,D] int8 or float8_e4m3fn; v [B,Lk,Hkv,D] bf16; scales fp32 [B,H,L]."""
+def attn_fwd(q: Tensor, k: Tensor, v: Tensor, scale_q: Tensor | None, scale_k: Tensor | None, causal: bool, acc16: int = 0) -> Tensor:
+    """q [B,Lq,Hq,D], k [B,Lk,Hkv,D]: int8 / float8_e4m3fn codes (optionally with fp32 scales [B,H,L]) or
+    bf16 / fp16; v [B,Lk,Hkv,D] bf16 or fp16 (the type of the output).  acc16: bit 0 = fp16 Q K^T
+    accumulation, bit 1 = fp16 P V accumulation (fp16 operands only)."""
     _need_cuda(q, k, v)
     B, Lq, Hq, D = q.shape
     _, Lk, Hkv, _ = k.shape
-    if q.dtype not in (torch.int8, torch.float8_e4m3fn) or k.dtype != q.dtype:
-        raise NotImplementedError(f"attention needs int8 or float8_e4m3fn Q and K (got {q.dtype}, {k.dtype})")
-    if v.dtype != torch.bfloat16:
-        raise NotImplementedError("attention needs bf16 V")
+    if q.dtype not in _ATTN_QK or k.dtype != q.dtype:
+        raise NotImplementedError(f"attention needs int8, float8_e4m3fn, bfloat16 or float16 Q and K of one type (got {q.dtype}, {k.dtype})")
+    if v.dtype not in (torch.bfloat16, torch.float16):
+        raise NotImplementedError("attention needs bf16 or fp16 V")
+    if q.dtype in (torch.bfloat16, torch.float16) and v.dtype != q.dtype:
+        raise NotImplementedError("16-bit Q and K need V of the same type")
     q = q if _blhd_ok(q) else q.contiguous()
     k = k if _blhd_ok(k) else k.contiguous()
     v = v if _blhd_ok(v) else v.contiguous()
     sq = scale_q.to(torch.float32).contiguous() if scale_q is not None else None
     sk = scale_k.to(torch.float32).contiguous() if scale_k is not None else None
-    o = torch.empty((B, Lq, Hq, D), dtype=torch.bfloat16, device=q.device)
+    o = torch.empty((B, Lq, Hq, D), dtype=v.dtype, device=q.device)
     I3 = ctypes.c_int64 * 3
     strides = [I3(*t.stride()[:3]) for t in (q, k, v, o)]
     with torch.cuda.device(q.device):
         check(
-            lib().gnk_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(sq), _p(sk), _QK[q.dtype], B, Lq, Lk, Hq, Hkv, D,
+            lib().gnk_attn_fwd(_p(q), _p(k), _p(v), _p(o), _p(sq), _p(sk), _ATTN_QK[q.dtype], _DT[v.dtype], acc16, B, Lq, Lk, Hq, Hkv, D,
                                strides[0], strides[1], strides[2], strides[3], int(causal), _stream(q)),
             "gnk_attn_fwd",
         )
@@ -352,9 +359,45 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, scale_q: Tensor | None, scale_k: T
 
 
 @attn_fwd.register_fake
-def _(q, k, v, scale_q, scale_k, causal):
+def _(q, k, v, scale_q, scale_k, causal, acc16=0):
     B, Lq, Hq, D = q.shape
-    return q.new_empty((B, Lq, Hq, D), dtype=torch.bfloat16)
+    return q.new_empty((B, Lq, Hq, D), dtype=v.dtype)
+
+
+def _lhd_ok(t: Tensor) -> bool:
+    es = t.element_size()
+    return t.stride(-1) == 1 and all((t.stride(i) * es) % 16 == 0 for i in range(2)) and t.data_ptr() % 16 == 0
+
+
+@torch.library.custom_op("gnk::attn_varlen_fwd", mutates_args=())
+def attn_varlen_fwd(q: Tensor, k: Tensor, v: Tensor, q_offsets: Tensor, kv_offsets: Tensor, max_q_len: int, causal: bool, acc16: int = 0) -> Tensor:
+    """Packed sequences: q [Lq_total,Hq,D], k / v [Lk_total,Hkv,D], all bf16 or all fp16; offsets int32 [B+1]."""
+    _need_cuda(q, k, v, q_offsets, kv_offsets)
+    Lq_total, Hq, D = q.shape
+    Lk_total, Hkv, _ = k.shape
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"packed attention needs bf16 or fp16 q, k, v of one type (got {q.dtype}, {k.dtype}, {v.dtype})")
+    q = q if _lhd_ok(q) else q.contiguous()
+    k = k if _lhd_ok(k) else k.contiguous()
+    v = v if _lhd_ok(v) else v.contiguous()
+    qo = q_offsets.to(torch.int32).contiguous()
+    ko = kv_offsets.to(torch.int32).contiguous()
+    B = qo.numel() - 1
+    o = torch.empty((Lq_total, Hq, D), dtype=v.dtype, device=q.device)
+    I2 = ctypes.c_int64 * 2
+    strides = [I2(*t.stride()[:2]) for t in (q, k, v, o)]
+    with torch.cuda.device(q.device):
+        check(
+            lib().gnk_attn_varlen_fwd(_p(q), _p(k), _p(v), _p(o), _p(qo), _p(ko), _ATTN_QK[q.dtype], acc16, B, max_q_len, Lq_total, Lk_total,
+                                      Hq, Hkv, D, strides[0], strides[1], strides[2], strides[3], int(causal), _stream(q)),
+            "gnk_attn_varlen_fwd",
+        )
+    return o
+
+
+@attn_varlen_fwd.register_fake
+def _(q, k, v, q_offsets, kv_offsets, max_q_len, causal, acc16=0):
+    return q.new_empty(q.shape, dtype=v.dtype)
 
 
 @torch.library.custom_op("gnk::mm_f8_block128", mutates_args=())

@@ -43,7 +43,7 @@ enum gnk_status {
 };
 
 enum gnk_dtype { GNK_BF16 = 0, GNK_F16 = 1, GNK_F32 = 2 };
-enum gnk_qkind { GNK_Q_INT8 = 0, GNK_Q_E4M3 = 1, GNK_Q_E5M2 = 2, GNK_Q_E2M1 = 3 };
+enum gnk_qkind { GNK_Q_INT8 = 0, GNK_Q_E4M3 = 1, GNK_Q_E5M2 = 2, GNK_Q_E2M1 = 3, GNK_Q_BF16 = 4, GNK_Q_F16 = 5 };
 enum gnk_mx_rule { GNK_MX_OCP = 0, GNK_MX_NV = 1 };
 enum gnk_out { GNK_OUT_BF16 = 0, GNK_OUT_I32 = 1 };
 
@@ -173,15 +173,35 @@ int gnk_mm_f8_block128(const void* A, int64_t lda, const float* SFA, int64_t ld_
 /* ------------------------------------------------------------------ attention ----- */
 
 /* Causal / full GQA attention forward, [B, L, H, D] layouts with D = 128 contiguous and
- * element strides given per tensor (batch, seq, head).  qk_kind: GNK_Q_E4M3 or GNK_Q_INT8
- * codes for Q and K with fp32 scales scale_q [B,Hq,Lq], scale_k [B,Hkv,Lk]; V and O bf16.
+ * element strides given per tensor (batch, seq, head).
+ *   qk_kind GNK_Q_E4M3 / GNK_Q_INT8: 8-bit codes for Q and K, with fp32 scales scale_q [B,Hq,Lq] and
+ *     scale_k [B,Hkv,Lk] (both or neither; INT8 accumulates exactly in int32);
+ *   qk_kind GNK_Q_BF16 / GNK_Q_F16: plain 16-bit Q and K, no scales, v_dtype must be the same type.
+ *   v_dtype GNK_BF16 / GNK_F16: type of V, of P (rounded before P*V) and of O.
+ *   acc16: bit 0 = Q*K^T accumulates in fp16, bit 1 = P*V accumulates in fp16 (fp16 operands only;
+ *     0 = fp32 accumulation).
  *   S = (q.k) * scale_q * scale_k * D^-1/2;  causal mask j <= i + (Lk - Lq);
- *   O = softmax(S) V with P rounded to bf16 before P*V; rows that see no key give 0.
- * Replaces: gn_kernels/triton_attn.py:268-325 `triton_attn` (scaled-QK path). */
+ *   O = softmax(S) V, softmax in fp32 with exp2; rows that see no key give 0.
+ * Replaces: gn_kernels/triton_attn.py:268-325 `triton_attn` (scaled path :316-320, unscaled :322,
+ * qk_fp16_acc / pv_fp16_acc :276-277,311-312). */
 int gnk_attn_fwd(const void* q, const void* k, const void* v, void* o, const float* scale_q,
-                 const float* scale_k, int qk_kind, int64_t B, int64_t Lq, int64_t Lk, int64_t Hq,
-                 int64_t Hkv, int64_t D, const int64_t* q_strides, const int64_t* k_strides,
+                 const float* scale_k, int qk_kind, int v_dtype, int acc16, int64_t B, int64_t Lq, int64_t Lk,
+                 int64_t Hq, int64_t Hkv, int64_t D, const int64_t* q_strides, const int64_t* k_strides,
                  const int64_t* v_strides, const int64_t* o_strides, int causal, gnk_stream_t stream);
+
+/* Same attention over packed variable-length sequences: q [Lq_total, Hq, D], k / v [Lk_total, Hkv, D],
+ * o [Lq_total, Hq, D], all bf16 or all fp16 (qk_kind GNK_Q_BF16 / GNK_Q_F16), D = 128 contiguous,
+ * strides (seq, head) in elements.  q_offsets / kv_offsets: int32 [B + 1] on the device, sequence b
+ * owns rows [offsets[b], offsets[b+1]); max_q_len bounds the longest query sequence (it sizes the
+ * grid).  The causal mask is lower-right aligned per sequence.  Tiles are loaded 128 rows at a time,
+ * so the last tile of a sequence also reads rows of its successor: they are masked out of the
+ * softmax, but a non-finite value in V there would still reach this sequence's output as NaN.
+ * Replaces: gn_kernels/triton_attn.py:462-517 `triton_varlen_attn`. */
+int gnk_attn_varlen_fwd(const void* q, const void* k, const void* v, void* o, const int32_t* q_offsets,
+                        const int32_t* kv_offsets, int qk_kind, int acc16, int64_t B, int64_t max_q_len,
+                        int64_t Lq_total, int64_t Lk_total, int64_t Hq, int64_t Hkv, int64_t D,
+                        const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                        const int64_t* o_strides, int causal, gnk_stream_t stream);
 
 /* ------------------------------------------------------------------ GEMM + RS ----- */
 

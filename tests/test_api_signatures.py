@@ -1,5 +1,5 @@
 """The Python entry points keep upstream's names, parameter names, order and defaults
-(gn_kernels/triton_mm.py:128, triton_attn.py:268, quant_utils.py:21-252,
+(gn_kernels/triton_mm.py:128, triton_attn.py:268 and :462, quant_utils.py:21-252,
 cutedsl/sm100/*.py `mm` / `gemm_rs`), so a caller switches packages without edits.  The
 expected signatures are written out here; nothing is imported from upstream."""
 
@@ -11,6 +11,8 @@ EXPECTED = {
     "triton_mm": (["A", "B", "bias", "scale_A", "scale_B", "out_dtype", "acc_dtype"], {"bias": None, "scale_A": None, "scale_B": None, "out_dtype": None, "acc_dtype": None}),
     "triton_attn": (["q", "k", "v", "scale_q", "scale_k", "causal", "qk_fp16_acc", "pv_fp16_acc"],
                     {"scale_q": None, "scale_k": None, "causal": False, "qk_fp16_acc": False, "pv_fp16_acc": False}),
+    "triton_varlen_attn": (["q", "k", "v", "q_offsets", "kv_offsets", "max_q_len", "causal", "qk_fp16_acc", "pv_fp16_acc"],
+                           {"causal": False, "qk_fp16_acc": False, "pv_fp16_acc": False}),
     "quantize_mx": (["x", "dtype", "compute_scale_method"], {"compute_scale_method": "ocp"}),
     "dequantize_mx": (["xq", "scales"], {}),
     "quantize_nvfp4": (["x", "tensor_scale", "eps"], {"tensor_scale": None, "eps": 1e-12}),

