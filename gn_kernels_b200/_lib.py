@@ -38,10 +38,12 @@ _SIGNATURES = {
     "gnk_sf_swizzle": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "gnk_dequant_block": (c_int, [_P, _P, c_int64, c_int64, c_int, c_int, _P, _P, _P]),
     "gnk_mm_bf16": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, _P]),
+    "gnk_mm_f16": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "gnk_mm_i8": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P, c_int, _P]),
     "gnk_mm_f8": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P, _P]),
     "gnk_mm_mxfp8": (c_int, [_P, c_int64, _P, c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "gnk_mm_nvfp4": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_float, _P, c_int64, c_int64, c_int64, c_int64, _P]),
+    "gnk_gated_mm_nvfp4": (c_int, [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, _P, c_int64, _P, c_int64, c_int64, c_int64, _P]),
     "gnk_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                              POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_int, _P]),
     "gnk_attn_varlen_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -121,6 +121,75 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   return GNK_OK;
 }
 
+// Persistent grid size of a kernel: the number of clusters that can be resident at once (cached per
+// instantiation and device by the caller).
+template <typename K>
+int resident_clusters(K kern, int cg, int threads, int smem_bytes, int* out) {
+  GNK_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  int n = num_sms() / cg;
+  if (cg > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_sms() / cg * cg));
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = cg;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int q = 0;
+    GNK_CUDA_OK(cudaOccupancyMaxActiveClusters(&q, kern, &cfg));
+    if (q > 0 && q < n) n = q;
+  }
+  *out = n;
+  return GNK_OK;
+}
+
+// Gated dual NVFP4 GEMM: X [M, K/2], W1 / W3 [N, K/2] packed E2M1; the B tile of output columns
+// [128 t, 128 t + 128) is rows of W1 followed by the same rows of W3.
+template <int CG>
+int launch_gated(const void* X, int64_t ldx, const uint8_t* SFX, const void* W1, const uint8_t* SFW1, const void* W3,
+                 const uint8_t* SFW3, int64_t ldw, GemmArgs g, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  using C = Cfg<MmaKind::MXF4NVF4, 256, CG, EPI_GATED, 0>;
+  const int64_t k_bytes = K / 2;
+  CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+  EpiMaps<EPI_GATED> maps;
+  const CUtensorMapDataType u8 = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  g.a_rows = M < 128 ? static_cast<int>((M + 7) / 8 * 8) : 128;
+  g.stages = C::stages_for(g.a_rows);
+  int rc = make_tmap_2d(&tm_a, u8, X, M, k_bytes, ldx, g.a_rows, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != GNK_OK) return rc;
+  if ((rc = make_tmap_2d(&tm_b, u8, W1, N, k_bytes, ldw, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != GNK_OK) return rc;
+  if ((rc = make_tmap_2d(&maps.b3, u8, W3, N, k_bytes, ldw, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != GNK_OK) return rc;
+  const int64_t atoms = ((K + 15) / 16 + 3) / 4;
+  const CUtensorMapDataType u64 = CU_TENSOR_MAP_DATA_TYPE_UINT64;
+  if ((rc = make_tmap_2d(&tm_sfa, u64, SFX, (M + 127) / 128, atoms * 64, atoms * 512, 1, C::kSfAtomBytes / 8, CU_TENSOR_MAP_SWIZZLE_NONE)) != GNK_OK) return rc;
+  if ((rc = make_tmap_2d(&tm_sfb, u64, SFW1, (N + 127) / 128, atoms * 64, atoms * 512, 1, C::kSfAtomBytes / 8, CU_TENSOR_MAP_SWIZZLE_NONE)) != GNK_OK) return rc;
+  if ((rc = make_tmap_2d(&maps.sfb3, u64, SFW3, (N + 127) / 128, atoms * 64, atoms * 512, 1, C::kSfAtomBytes / 8, CU_TENSOR_MAP_SWIZZLE_NONE)) != GNK_OK) return rc;
+  maps.c = tm_a;
+  g.k_iters = static_cast<int>((k_bytes + 127) / 128);
+  g.tiles_m = static_cast<int>((M + 128 * CG - 1) / (128 * CG));
+  g.tiles_n = static_cast<int>(N / 128);
+  auto kern = gemm_kernel<MmaKind::MXF4NVF4, 256, CG, EPI_GATED, 0>;
+  static int resident[64];
+  int dev = 0;
+  GNK_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return GNK_ERR_UNSUPPORTED;
+  if (resident[dev] == 0) {
+    int n = 0;
+    if ((rc = resident_clusters(kern, CG, 192, C::kSmemBytes, &n)) != GNK_OK) return rc;
+    resident[dev] = n;
+  }
+  int clusters = resident[dev];
+  const int tiles = g.tiles_m * g.tiles_n;
+  if (clusters > tiles) clusters = tiles;
+  kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, maps, g);
+  GNK_LAUNCH_OK();
+  return GNK_OK;
+}
+
 // Tile choice: the largest tile that still gives every SM work; 2-CTA 256x256 for big problems.
 enum TileSel { T_2x256, T_1x256, T_1x128, T_1x64 };
 std::atomic<int> g_force_tile{-1};  // test hook (gnk_debug_force_tile)
@@ -216,6 +285,17 @@ extern "C" int gnk_mm_bf16(const void* A, int64_t lda, const void* Bt, int64_t l
                                                static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int gnk_mm_f16(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc, int64_t M,
+                          int64_t N, int64_t K, int acc_f16, gnk_stream_t stream) {
+  int rc = check_common(A, Bt, C, M, N, K, lda * 2, ldb * 2);
+  if (rc != GNK_OK) return rc;
+  if (K % 8 != 0) return GNK_ERR_BAD_SHAPE;
+  GemmArgs g = base_args(C, ldc, M, N, 2);
+  g.f16 = 1 | 4 | (acc_f16 ? 2 : 0);
+  return dispatch_tile<MmaKind::F16, EPI_BF16>(A, lda, Bt, ldb, nullptr, nullptr, g, M, N, K,
+                                               static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int gnk_mm_i8(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc, int64_t M,
                          int64_t N, int64_t K, const float* scale_A, const float* scale_B, const float* bias,
                          int out_kind, gnk_stream_t stream) {
@@ -261,6 +341,32 @@ extern "C" int gnk_mm_mxfp8(const void* A, int64_t lda, const void* Bt, int64_t 
   GemmArgs g = base_args(C, ldc, M, N, 2);
   return dispatch_tile<MmaKind::MXF8F6F4, EPI_BF16>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K,
                                                     static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gnk_gated_mm_nvfp4(const void* X, int64_t ldx, const uint8_t* SFX, const float* ts_x, const void* W1,
+                                  const uint8_t* SFW1, const float* ts_w1, const void* W3, const uint8_t* SFW3,
+                                  const float* ts_w3, int64_t ldw, const float* ts_out, void* C, int64_t ldc, uint8_t* SFC,
+                                  int64_t M, int64_t N, int64_t K, gnk_stream_t stream) {
+  if (!W3 || !SFX || !SFW1 || !SFW3 || !ts_x || !ts_w1 || !ts_w3) return GNK_ERR_BAD_ARG;
+  int rc = check_common(X, W1, C, M, N, K, ldx, ldw);
+  if (rc != GNK_OK) return rc;
+  if (!aligned16(W3) || !aligned16(SFX) || !aligned16(SFW1) || !aligned16(SFW3) || !aligned16(C)) return GNK_ERR_BAD_ALIGN;
+  if (K % 32 != 0 || N % 128 != 0) return GNK_ERR_BAD_SHAPE;
+  if ((ts_out != nullptr) != (SFC != nullptr)) return GNK_ERR_BAD_ARG;
+  if (ts_out ? (ldc % 8 != 0 || (reinterpret_cast<uintptr_t>(SFC) & 3)) : (ldc % 8 != 0)) return GNK_ERR_BAD_ALIGN;
+  GemmArgs g = base_args(C, ldc, M, N, 2);
+  g.gated.ts_x = ts_x;
+  g.gated.ts_w1 = ts_w1;
+  g.gated.ts_w3 = ts_w3;
+  g.gated.ts_out = ts_out;
+  g.gated.sfc = SFC;
+  g.gated.eps = 1e-12f;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // pair tiles (256 rows) once they give every SM work, single-CTA 128-row tiles below that
+  const int64_t pair_ctas = ((M + 255) / 256) * (N / 128) * 2;
+  if (g_force_tile.load() != 1 && (g_force_tile.load() == 0 || pair_ctas >= num_sms()))
+    return launch_gated<2>(X, ldx, SFX, W1, SFW1, W3, SFW3, ldw, g, M, N, K, st);
+  return launch_gated<1>(X, ldx, SFX, W1, SFW1, W3, SFW3, ldw, g, M, N, K, st);
 }
 
 extern "C" int gnk_mm_nvfp4(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA,

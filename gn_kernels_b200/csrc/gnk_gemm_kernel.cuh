@@ -2,12 +2,12 @@
 // GEMM + reduce-scatter.  See gnk_gemm.cu for the description of the warp roles.
 #pragma once
 
-#include "gnk_common.cuh"
+#include "gnk_quant_math.cuh"
 
 namespace gnk {
 namespace gemm {
 
-enum Epi { EPI_BF16 = 0, EPI_ROWSCALED = 1, EPI_I32 = 2, EPI_RS = 3 };
+enum Epi { EPI_BF16 = 0, EPI_ROWSCALED = 1, EPI_I32 = 2, EPI_RS = 3, EPI_GATED = 4 };
 constexpr int kMaxWorld = 8;  // ranks of one NVLink domain the reduce-scatter variant addresses
 constexpr int kTraceEvents = 256;  // stages recorded per (CTA, role) when tracing
 
@@ -33,6 +33,20 @@ struct GemmArgs {
   long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
   int a_rows;        // rows of A one stage load brings in (the tensor map's box; 128 unless M < 128)
   int stages;        // pipeline depth (the launcher's choice: fewer A rows per stage leave room for more stages)
+  int f16;           // kind::f16 only: bit 0 = operands are fp16 (else bf16), bit 1 = fp16 accumulator, bit 2 = fp16 output
+  // Gated dual GEMM (EPI_GATED): the B tile holds 128 rows of W1 and the matching 128 rows of W3, so
+  // accumulator columns [0,128) are X W1^T and [128,256) X W3^T for the same 128 output columns.
+  // out = (o1 * o3) * sigmoid(o1) with o1 = acc1 * (ts_w1 * ts_x), o3 = acc3 * (ts_w3 * ts_x); written
+  // as bf16 (C, ldc in elements), or, when ts_out is set, quantised to NVFP4 (C = packed E2M1, ldc in
+  // bytes; sfc = E4M3 block scales in the swizzled layout with N/16 columns).
+  struct {
+    const float* ts_x;
+    const float* ts_w1;
+    const float* ts_w3;
+    const float* ts_out;
+    uint8_t* sfc;
+    float eps;
+  } gated;
   // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
   // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
   // THIS GPU.  Flag words: one per owned 128 x BN unit, then a CTA ticket, then the exit counter.
@@ -66,6 +80,12 @@ struct EpiMaps<EPI_RS> {
   CUtensorMap slot[kMaxWorld];
   CUtensorMap local;  // pull variant: this rank's own [M, N] partial
 };
+template <>
+struct EpiMaps<EPI_GATED> {
+  CUtensorMap c;     // unused
+  CUtensorMap b3;    // W3 [N, K] (tm_b is W1), 128-row boxes
+  CUtensorMap sfb3;  // its scale atoms (tm_sfb is W1's), one 128-row group per box
+};
 template <int EPI>
 __device__ __forceinline__ const CUtensorMap* output_map(const EpiMaps<EPI>& m) {
   return &m.c;
@@ -83,7 +103,7 @@ struct Cfg {
   // so only 32 KB of pipeline space is given up.  The reduce-scatter variant stages the whole
   // 32 x 256 piece (16 KB per warp) because it waits for completion once per tile.
   static constexpr bool kStaged = EPI == EPI_RS && BN == 256 && CG == 2;
-  static constexpr bool kBulkC = STG != 0 && BN == 256 && CG == 2 && EPI != EPI_I32 && EPI != EPI_RS;
+  static constexpr bool kBulkC = STG != 0 && BN == 256 && CG == 2 && EPI != EPI_I32 && EPI != EPI_RS && EPI != EPI_GATED;
   static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : kBulkC ? 4 * 2 * 4096 : 0;
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = (BN / CG) * 128;
@@ -207,6 +227,10 @@ __device__ __forceinline__ void finish_cols(const uint32_t* r, const GemmArgs& g
 #pragma unroll
   for (int i = 0; i < W; ++i) {
     float v = KIND == MmaKind::I8 ? static_cast<float>(static_cast<int32_t>(r[i])) : __uint_as_float(r[i]);
+    if constexpr (KIND == MmaKind::F16 && EPI == EPI_BF16) {
+      // an fp16 accumulator sits in the low half of its 32-bit TMEM column
+      if (g.f16 & 2) v = __half2float(__ushort_as_half(static_cast<unsigned short>(r[i] & 0xFFFFu)));
+    }
     if constexpr (EPI == EPI_ROWSCALED) {
       const int c = min(col0 + i, g.N - 1);
       if (g.scale_a) v = __fmul_rn(v, sa);
@@ -217,6 +241,18 @@ __device__ __forceinline__ void finish_cols(const uint32_t* r, const GemmArgs& g
     }
     f[i] = v;
   }
+}
+
+// two finished values -> one 32-bit word of the 16-bit output type (bf16, or fp16 for the fp16 GEMM)
+template <MmaKind KIND, int EPI>
+__device__ __forceinline__ uint32_t pack_out(const GemmArgs& g, float lo, float hi) {
+  if constexpr (KIND == MmaKind::F16 && EPI == EPI_BF16) {
+    if (g.f16 & 4) {
+      __half2 h = __floats2half2_rn(lo, hi);
+      return *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+  return pack_bf16x2(lo, hi);
 }
 
 // ---- epilogue: W (16 or 32) consecutive accumulator columns of one row ------------------
@@ -240,10 +276,12 @@ __device__ __forceinline__ void store_cols(const uint32_t* r, const GemmArgs& g,
     if (full) {
 #pragma unroll
       for (int i = 0; i < W; i += 8)
-        *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack_bf16x2(f[i], f[i + 1]), pack_bf16x2(f[i + 2], f[i + 3]),
-                                                        pack_bf16x2(f[i + 4], f[i + 5]), pack_bf16x2(f[i + 6], f[i + 7]));
+        *reinterpret_cast<uint4*>(dst + i) =
+            make_uint4(pack_out<KIND, EPI>(g, f[i], f[i + 1]), pack_out<KIND, EPI>(g, f[i + 2], f[i + 3]),
+                       pack_out<KIND, EPI>(g, f[i + 4], f[i + 5]), pack_out<KIND, EPI>(g, f[i + 6], f[i + 7]));
     } else {
-      for (int i = 0; i < W && col0 + i < g.N; ++i) dst[i] = __float2bfloat16_rn(f[i]);
+      for (int i = 0; i < W && col0 + i < g.N; ++i)
+        reinterpret_cast<uint16_t*>(dst)[i] = static_cast<uint16_t>(pack_out<KIND, EPI>(g, f[i], 0.f) & 0xFFFFu);
     }
   }
 }
@@ -350,11 +388,89 @@ __device__ __forceinline__ void drain_to_smem_sw128(uint32_t taddr_row, int c0, 
     for (int j = 0; j < 2; ++j) {
       const int piece = (c >> 3) + j;  // 16-byte piece of the row
       const uint32_t addr = stg + (piece >> 3) * blk_stride + r * 128 + (((piece & 7) ^ (r & 7)) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(f[8 * j], f[8 * j + 1])),
-                   "r"(pack_bf16x2(f[8 * j + 2], f[8 * j + 3])), "r"(pack_bf16x2(f[8 * j + 4], f[8 * j + 5])),
-                   "r"(pack_bf16x2(f[8 * j + 6], f[8 * j + 7]))
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_out<KIND, EPI>(g, f[8 * j], f[8 * j + 1])),
+                   "r"(pack_out<KIND, EPI>(g, f[8 * j + 2], f[8 * j + 3])), "r"(pack_out<KIND, EPI>(g, f[8 * j + 4], f[8 * j + 5])),
+                   "r"(pack_out<KIND, EPI>(g, f[8 * j + 6], f[8 * j + 7]))
                    : "memory");
     }
+  }
+}
+
+// Epilogue of the gated dual GEMM for one thread (= one output row): 128 output columns in eight
+// 16-column chunks, each from 16 columns of X W1^T (accumulator columns c..c+15) and the matching 16
+// of X W3^T (128 + c..).  The chunks whose accumulator columns are shared with the other TMEM
+// accumulator are taken first and released at once (acc 0 shares its last 48 columns, the X W3^T
+// chunks 5-7; acc 1 its first 48, the X W1^T chunks 0-2).  bf16 output: 32 bytes per chunk.  NVFP4
+// output: a chunk is exactly one scale block, quantised from the bf16-rounded values with the
+// quantizer's own arithmetic, 8 bytes of codes per chunk and the eight scale bytes of the row in
+// two 4-byte stores (the swizzled layout keeps four consecutive blocks of a row together).
+template <int BN, int ACC_STRIDE, int OVERLAP_COLS>
+__device__ __forceinline__ void gated_epilogue(uint32_t taddr_row, uint32_t acc, const GemmArgs& g, int row, int ocol0,
+                                               uint32_t partial_bar, uint32_t tempty_bar, int lane) {
+  static_assert(BN == 256 && OVERLAP_COLS == 48 && ACC_STRIDE == 208, "chunk order below is written for the NVFP4 256-wide tile");
+  const float a1 = __fmul_rn(__ldg(g.gated.ts_w1), __ldg(g.gated.ts_x));
+  const float a3 = __fmul_rn(__ldg(g.gated.ts_w3), __ldg(g.gated.ts_x));
+  const bool fp4 = g.gated.ts_out != nullptr;
+  float ts = 0.f, d0 = 1.f, r0 = 1.f;
+  if (fp4) {
+    ts = __ldg(g.gated.ts_out);
+    d0 = fmaxf(__fmul_rn(6.f, ts), 1e-12f);
+    r0 = __frcp_rn(d0);
+  }
+  const bool live = row < g.M;
+  uint32_t sf_lo = 0, sf_hi = 0;  // scale codes of chunks 0-3 and 4-7
+  const int first = acc == 0 ? 5 : 0;
+#pragma unroll 1
+  for (int idx = 0; idx < 8; ++idx) {
+    const int c = (first + idx) & 7;
+    uint32_t r1[16], r3[16];
+    tmem_ld16(taddr_row + c * 16, r1);
+    tmem_ld16(taddr_row + 128 + c * 16, r3);
+    tc_wait_ld();
+    if (idx == 2) {  // the three chunks read so far covered every column shared with the other accumulator
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(partial_bar);
+    }
+    float f[2][8];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float o1 = __fmul_rn(__uint_as_float(r1[i]), a1);
+      const float o3 = __fmul_rn(__uint_as_float(r3[i]), a3);
+      const float sig = __frcp_rn(1.f + __expf(-o1));
+      f[i >> 3][i & 7] = __fmul_rn(__fmul_rn(o1, o3), sig);
+    }
+    if (!fp4) {
+      if (live) {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.C) + static_cast<int64_t>(row) * g.ldc + ocol0 + c * 16;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(pack_bf16x2(f[j][0], f[j][1]), pack_bf16x2(f[j][2], f[j][3]),
+                                                              pack_bf16x2(f[j][4], f[j][5]), pack_bf16x2(f[j][6], f[j][7]));
+      }
+    } else {
+      // the quantizer sees the bf16 output, exactly as a separate quantizer kernel after this GEMM would
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[j][i] = __bfloat162float(__float2bfloat16_rn(f[j][i]));
+      uint32_t code;
+      const uint2 q = nvfp4_encode16(f, ts, d0, r0, g.gated.eps, code);
+      if (live)
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(g.C) + static_cast<int64_t>(row) * g.ldc + (ocol0 + c * 16) / 2) = q;
+      if (c < 4) sf_lo |= code << (8 * c);
+      else sf_hi |= code << (8 * (c - 4));
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive_cluster(tempty_bar);
+  if (fp4 && live) {
+    const int64_t ks = g.N >> 4;  // scale columns of the output (N % 128 == 0, so no padding columns)
+    const int64_t kcol0 = ocol0 >> 4;
+    uint8_t* sfc = g.gated.sfc;
+    *reinterpret_cast<uint32_t*>(sfc + sf_offset(row, kcol0, ks, true, ks)) = sf_lo;
+    *reinterpret_cast<uint32_t*>(sfc + sf_offset(row, kcol0 + 4, ks, true, ks)) = sf_hi;
   }
 }
 
@@ -420,6 +536,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       tma_prefetch_desc(&tm_sfa);
       tma_prefetch_desc(&tm_sfb);
     }
+    if constexpr (EPI == EPI_GATED) {
+      tma_prefetch_desc(&epi_maps.b3);
+      tma_prefetch_desc(&epi_maps.sfb3);
+    }
   }
   if (warp == 5) {
     tmem_alloc<CG>(tmem_slot, C::kTmemCols);
@@ -463,7 +583,27 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         const uint32_t full = full0 + 8 * stage;
         const uint32_t sa = stage_a(stage), sb = stage_b(stage);
         if (leader) {
-          if constexpr (CG == 2) {
+          if constexpr (EPI == EPI_GATED) {
+            // 128 rows of W1 and the same 128 rows of W3 form the 256-row B tile; with a CTA pair each
+            // CTA fetches one of them, and both fetch both scale-atom groups
+            const int w_row = tn * 128;
+            if constexpr (CG == 2) {
+              mbar_expect_tx_cluster(full, stage_tx);
+              tma_load_2d_pair(sa, &tm_a, full, k * kInner, a_row);
+              tma_load_2d_pair(sb, cta_rank == 0 ? &tm_b : &epi_maps.b3, full, k * kInner, w_row);
+              tma_load_2d_pair(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
+              tma_load_2d_pair(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), tn);
+              tma_load_2d_pair(stage_sfb(stage) + C::kSfAtomBytes, &epi_maps.sfb3, full, k * (C::kSfAtomBytes / 8), tn);
+            } else {
+              mbar_expect_tx(full, stage_tx);
+              tma_load_2d(sa, &tm_a, full, k * kInner, a_row);
+              tma_load_2d(sb, &tm_b, full, k * kInner, w_row);
+              tma_load_2d(sb + 128 * 128, &epi_maps.b3, full, k * kInner, w_row);
+              tma_load_2d(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
+              tma_load_2d(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), tn);
+              tma_load_2d(stage_sfb(stage) + C::kSfAtomBytes, &epi_maps.sfb3, full, k * (C::kSfAtomBytes / 8), tn);
+            }
+          } else if constexpr (CG == 2) {
             mbar_expect_tx_cluster(full, stage_tx);
             tma_load_2d_pair(sa, &tm_a, full, k * kInner, a_row);
             tma_load_2d_pair(sb, &tm_b, full, k * kInner, b_row);
@@ -501,6 +641,11 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
                                   : KIND == MmaKind::F8F6F4 ? idesc_dense(1, 0, 0, 128 * CG, BN)
                                   : KIND == MmaKind::MXF8F6F4 ? idesc_block_scaled(0, 1, 128 * CG, BN)
                                                               : idesc_block_scaled(1, 0, 128 * CG, BN);
+      uint32_t idesc = kIdesc;
+      if constexpr (KIND == MmaKind::F16 && EPI == EPI_BF16) {
+        if (g.f16 & 1) idesc &= ~((7u << 7) | (7u << 10));  // operand formats: F16 = 0 (BF16 = 1)
+        if (g.f16 & 2) idesc &= ~(3u << 4);                 // accumulator format: F16 = 0 (F32 = 1)
+      }
       const uint32_t sf_tmem = tmem_base + C::kSfBase;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
         if (!mbar_wait(bar_tempty(acc), acc_parity, (2u << 24) | (2u << 16) | acc)) { ok = false; break; }
@@ -542,14 +687,14 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
             for (int kk = 0; kk < 4; ++kk) {
               const uint32_t accum = (k | kk) != 0;
               if constexpr (!kBS) {
-                tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, accum);
+                tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accum);
               } else if constexpr (KIND == MmaKind::MXF8F6F4) {
                 // the four K steps of a stage read bytes 0..3 of the same scale columns (scale ids in the descriptor)
-                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc | (kk << 4) | (kk << 29), sf_tmem,
+                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc | (kk << 4) | (kk << 29), sf_tmem,
                                     sf_tmem + C::kSfaCols + sfb_half, accum);
               } else {
                 // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
-                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, sf_tmem + 4 * kk,
+                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, sf_tmem + 4 * kk,
                                     sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4 + sfb_half, accum);
               }
             }
@@ -662,6 +807,8 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
             tma_store_commit();
           }
         }
+      } else if constexpr (EPI == EPI_GATED) {
+        gated_epilogue<BN, C::kAccStride, C::kOverlapCols>(taddr_row, acc, g, row, tn * 128, partial, tempty0 + 8 * acc, lane);
       } else {
       if constexpr (C::kOverlap) {
         // the columns shared with the other accumulator go first and are released at once

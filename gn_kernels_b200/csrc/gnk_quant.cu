@@ -2,87 +2,15 @@
 // (E4M3 per 16 + fp32 tensor scale), scale-factor swizzle, block dequantizer.
 //
 // All of them are one-pass, HBM-bound byte producers: 128-bit loads, block maxima in
-// registers (shuffles only where a block spans lanes), 64/128-bit stores.  Results must
-// equal the torch reference bit for bit, which fixes two things:
-//   * quotients are correctly rounded fp32 divisions.  divide_exact() gets them with one
-//     correctly rounded reciprocal per block and two FMA residual corrections per element
-//     (Markstein's theorem: a faithful quotient corrected once with an exactly computed
-//     residual and a correctly rounded reciprocal is the correctly rounded quotient; the
-//     first correction makes the estimate faithful, the second makes it exact);
-//   * narrow formats are produced by the cvt.rn.satfinite instructions, which round to
-//     nearest even exactly like the reference's casts and threshold chains.
+// registers (shuffles only where a block spans lanes), 64/128-bit stores, packed f32x2 arithmetic.
+// The arithmetic that makes the bytes equal the torch reference bit for bit lives in gnk_quant_math.cuh.
 #include <mutex>
 #include <type_traits>
 
-#include "gnk_common.cuh"
+#include "gnk_quant_math.cuh"
 
 namespace gnk {
 namespace {
-
-// x / d for d > 0, given r = __frcp_rn(d).  Correctly rounded when the quotient is far
-// from overflow and x is not within 2^-100 of zero (then the result only feeds a
-// rounding to zero); `safe` = false takes the plain IEEE division instead.
-__device__ __forceinline__ float divide_exact(float x, float d, float r, bool safe) {
-  if (!safe) return __fdiv_rn(x, d);
-  float q = __fmul_rn(x, r);
-  float e = __fmaf_rn(-d, q, x);
-  q = __fmaf_rn(e, r, q);
-  e = __fmaf_rn(-d, q, x);
-  q = __fmaf_rn(e, r, q);
-  return copysignf(q, x);  // x = -0 must stay -0 (the packers copy the sign bit)
-}
-
-__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {  // low byte <- lo
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-__device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-// 8 floats -> 8 E2M1 codes in 4 bytes; element 2i goes to the HIGH nibble of byte i.
-__device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&v)[8]) {
-  uint32_t r;
-  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b0, %1, %2;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b1, %3, %4;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b2, %5, %6;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b3, %7, %8;\n\t"
-      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
-      : "=r"(r)
-      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
-  return r;
-}
-__device__ __forceinline__ float e4m3_to_f32(uint32_t code) {
-  uint32_t h2;
-  uint16_t c = static_cast<uint16_t>(code & 0xFF);
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(c));
-  return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xFFFF)));
-}
-__device__ __forceinline__ float e5m2_to_f32(uint32_t code) {
-  return __half2float(__ushort_as_half(static_cast<unsigned short>((code & 0xFF) << 8)));
-}
-__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
-  const float mag = (code & 4) ? ((code & 2) ? ((code & 1) ? 6.f : 4.f) : ((code & 1) ? 3.f : 2.f))
-                               : ((code & 2) ? ((code & 1) ? 1.5f : 1.f) : ((code & 1) ? .5f : 0.f));
-  return (code & 8) ? -mag : mag;
-}
-
-__device__ __forceinline__ float amax8(const float (&v)[8]) {
-  float m = fabsf(v[0]);
-#pragma unroll
-  for (int i = 1; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
-  return m;
-}
-
-__device__ __forceinline__ size_t sf_offset(int64_t row, int64_t kcol, int64_t ks_padded, bool swizzled,
-                                            int64_t ks) {
-  if (!swizzled) return static_cast<size_t>(row * ks + kcol);
-  const int64_t mb = row >> 7, r = row & 127;
-  return static_cast<size_t>(((mb * (ks_padded >> 2) + (kcol >> 2)) * 32 + (r & 31)) * 16 + (r >> 5) * 4 + (kcol & 3));
-}
 
 // ------------------------------------------------------------------------------------
 // per-tensor absmax: partial maxima per CTA in scratch, last CTA (ticket) folds them
@@ -209,8 +137,7 @@ __global__ void __launch_bounds__(256) quant_rowwise_kernel(const T* __restrict_
     }
     uint8_t* qr = q + row * cols;
     auto encode = [&](float (&v)[8], int64_t c) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = divide_exact(v[i], d, r, safe);
+      divide_exact8(v, d, r, safe);
       uint2 out;
       if constexpr (QKIND == GNK_Q_INT8) {
         uint32_t b[8];
@@ -247,17 +174,98 @@ __global__ void __launch_bounds__(256) quant_rowwise_kernel(const T* __restrict_
   }
 }
 
+// Row-wise quantizer for rows of up to G * 32 elements: G threads share a row and hold it in registers
+// (up to four 8-element groups each, group j of thread `sub` at column (j * G + sub) * 8, so a warp's
+// loads are contiguous), so x is read from memory exactly once.  G <= 32: the row maximum is folded by
+// shuffles; larger G: through shared memory.
+template <int QKIND>
+__device__ __forceinline__ void rowwise_encode8(float (&v)[8], float d, float r, bool safe, uint8_t* dst) {
+  divide_exact8(v, d, r, safe);
+  uint2 out;
+  if constexpr (QKIND == GNK_Q_INT8) {
+    uint32_t b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float t = fminf(fmaxf(rintf(v[i]), -128.f), 127.f);
+      b[i] = static_cast<uint32_t>(static_cast<int>(t)) & 0xFFu;
+    }
+    out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+  } else {
+    out.x = cvt_e4m3x2(v[0], v[1]) | (cvt_e4m3x2(v[2], v[3]) << 16);
+    out.y = cvt_e4m3x2(v[4], v[5]) | (cvt_e4m3x2(v[6], v[7]) << 16);
+  }
+  *reinterpret_cast<uint2*>(dst) = out;
+}
+
+template <typename T, int QKIND, int G>
+__global__ void __launch_bounds__(256) quant_rowwise_reg_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
+                                                                int64_t ldx, uint8_t* __restrict__ q,
+                                                                float* __restrict__ scale, int64_t perm_h,
+                                                                int64_t perm_l) {
+  constexpr int kRowsPerCta = 256 / G;
+  constexpr int kWarpsPerRow = G > 32 ? G / 32 : 1;
+  __shared__ float warp_max[8];
+  const int sub = threadIdx.x % G;
+  const float qmax = QKIND == GNK_Q_INT8 ? 127.f : 448.f;
+  for (int64_t rg = blockIdx.x; rg * kRowsPerCta < rows; rg += gridDim.x) {
+    const int64_t row = rg * kRowsPerCta + threadIdx.x / G;
+    const bool live = row < rows;
+    const T* xr = x + (live ? row : 0) * ldx;
+    float v[4][8];
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t c = static_cast<int64_t>(j * G + sub) * 8;
+      if (live && c < cols) {
+        load8<T>(xr + c, v[j]);
+        m = fmaxf(m, amax8(v[j]));
+      }
+    }
+#pragma unroll
+    for (int o = (G < 32 ? G : 32) / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if constexpr (G > 32) {
+      __syncthreads();  // the previous row group's maxima have been read
+      if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+      __syncthreads();
+      const int w0 = (threadIdx.x >> 5) / kWarpsPerRow * kWarpsPerRow;
+      m = warp_max[w0];
+#pragma unroll
+      for (int i = 1; i < kWarpsPerRow; ++i) m = fmaxf(m, warp_max[w0 + i]);
+    }
+    if (!live) continue;
+    const float s = __fdiv_rn(m, qmax);
+    const float d = fmaxf(s, 1e-6f);
+    const float r = __frcp_rn(d);
+    const bool safe = m >= 1e-30f;  // quotients are <= qmax * (1 + eps) then; tiny rows take the slow path
+    if (sub == 0) {
+      int64_t idx = row;
+      if (perm_h > 0) {
+        const int64_t h = row % perm_h, bl = row / perm_h, l = bl % perm_l, b = bl / perm_l;
+        idx = (b * perm_h + h) * perm_l + l;
+      }
+      scale[idx] = s;
+    }
+    uint8_t* qr = q + row * cols;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t c = static_cast<int64_t>(j * G + sub) * 8;
+      if (c < cols) rowwise_encode8<QKIND>(v[j], d, r, safe, qr + c);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // MX quantizer: one thread per 32-element block
 // ------------------------------------------------------------------------------------
 template <typename T, int QKIND, int RULE>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
                                                        uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
-                                                       int swizzled, int64_t rows_out, int64_t ks_out) {
+                                                       int swizzled, int64_t rows_out, int64_t ks_out, int ks_shift) {
   const int64_t ks = K >> 5;
   const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;  // the launcher keeps rows_out * ks_out below 2^31
   if (idx >= static_cast<unsigned>(rows_out * ks_out)) return;
-  const unsigned urow = idx / static_cast<unsigned>(ks_out);
+  const unsigned urow = ks_shift >= 0 ? idx >> ks_shift : idx / static_cast<unsigned>(ks_out);
   const int64_t row = urow, kb = idx - urow * static_cast<unsigned>(ks_out);
   if (row >= M || kb >= ks) {  // padding of the swizzled layout
     sf[sf_offset(row, kb, ks_out, true, ks)] = 0;
@@ -287,13 +295,20 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const T* __restrict__ x, 
   const bool clipped = !(denom >= 1e-12f);
   // 1 / 2^(e-127) is exact (a subnormal for e = 254), so the product equals the quotient
   const float recip = __uint_as_float(ebits >= 254 ? 0x00400000u : (254u - ebits) << 23);
+  // The clip to +-kAmax of the reference is what the saturating conversions below do for every
+  // finite value, so only the scaling is left here.
+  if (clipped) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float y = clipped ? __fdiv_rn(v[j][i], 1e-12f) : __fmul_rn(v[j][i], recip);
-      v[j][i] = fminf(fmaxf(y, -kAmax), kAmax);
-    }
+      for (int i = 0; i < 8; ++i) v[j][i] = fminf(fmaxf(__fdiv_rn(v[j][i], 1e-12f), -kAmax), kAmax);
+  } else {
+    const uint64_t recip2 = f2_pack(recip, recip);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) f2_unpack(f2_mul(f2_pack(v[j][i], v[j][i + 1]), recip2), v[j][i], v[j][i + 1]);
+  }
   if constexpr (QKIND == GNK_Q_E2M1) {
     uint4 out = make_uint4(cvt_e2m1x8(v[0]), cvt_e2m1x8(v[1]), cvt_e2m1x8(v[2]), cvt_e2m1x8(v[3]));
     *reinterpret_cast<uint4*>(q + row * (K >> 1) + kb * 16) = out;
@@ -322,11 +337,11 @@ template <typename T>
 __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
                                                           const float* __restrict__ tensor_scale, float eps,
                                                           uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
-                                                          int swizzled, int64_t rows_out, int64_t ks_out) {
+                                                          int swizzled, int64_t rows_out, int64_t ks_out, int ks_shift) {
   const int64_t ks = K >> 4;
   const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;  // the launcher keeps rows_out * ks_out below 2^31
   if (idx >= static_cast<unsigned>(rows_out * ks_out)) return;
-  const unsigned urow = idx / static_cast<unsigned>(ks_out);
+  const unsigned urow = ks_shift >= 0 ? idx >> ks_shift : idx / static_cast<unsigned>(ks_out);
   const int64_t row = urow, kb = idx - urow * static_cast<unsigned>(ks_out);
   if (row >= M || kb >= ks) {
     sf[sf_offset(row, kb, ks_out, true, ks)] = 0;
@@ -336,24 +351,12 @@ __global__ void __launch_bounds__(256) quant_nvfp4_kernel(const T* __restrict__ 
   float v[2][8];
   load8<T>(p, v[0]);
   load8<T>(p + 8, v[1]);
-  const float m = fmaxf(amax8(v[0]), amax8(v[1]));
   const float ts = __ldg(tensor_scale);
-
   const float d0 = fmaxf(__fmul_rn(6.f, ts), 1e-12f);
-  const float s32 = fminf(__fdiv_rn(m, d0), 448.f);
-  const uint32_t code = cvt_e4m3x2(s32, 0.f) & 0xFFu;
+  const float r0 = __frcp_rn(d0);
+  uint32_t code;
+  const uint2 out = nvfp4_encode16(v, ts, d0, r0, eps, code);
   sf[sf_offset(row, kb, ks_out, swizzled != 0, ks)] = static_cast<uint8_t>(code);
-
-  const float d1 = fmaxf(__fmul_rn(ts, e4m3_to_f32(code)), eps);
-  const float r = __frcp_rn(d1);
-  // |x| <= m, so every quotient is below m * r * (1 + 2^-22); keep far from overflow, and
-  // keep d1 / r in the normal range so the residuals are exact
-  const bool safe = (m * r < 1e30f) && (d1 > 1e-30f) && (d1 < 1e30f);
-#pragma unroll
-  for (int j = 0; j < 2; ++j)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[j][i] = divide_exact(v[j][i], d1, r, safe);
-  uint2 out = make_uint2(cvt_e2m1x8(v[0]), cvt_e2m1x8(v[1]));
   *reinterpret_cast<uint2*>(q + row * (K >> 1) + kb * 8) = out;
 }
 
@@ -391,6 +394,14 @@ __global__ void dequant_block_kernel(const uint8_t* __restrict__ q, const uint8_
   float sv = block == 32 ? __uint_as_float(s << 23) : e4m3_to_f32(s);
   if (tensor_scale) sv = __fmul_rn(sv, __ldg(tensor_scale));
   out[i] = __fmul_rn(v, sv);
+}
+
+// log2(n) when n is a power of two (the kernels then index with a shift instead of a division), else -1
+inline int pow2_shift(int64_t n) {
+  if (n <= 0 || (n & (n - 1))) return -1;
+  int s = 0;
+  while ((int64_t{1} << s) < n) ++s;
+  return s;
 }
 
 template <typename F>
@@ -432,8 +443,22 @@ extern "C" int gnk_absmax(const void* x, int dtype, int64_t n, float divisor, fl
 template <typename T, int QKIND>
 static int launch_rowwise(const T* x, int64_t rows, int64_t cols, int64_t ldx, uint8_t* q, float* scale,
                           int64_t perm_h, int64_t perm_l, cudaStream_t st) {
-  int lpr = 32;
-  while (lpr > 1 && (lpr / 2) * 8 >= cols) lpr /= 2;
+  const int64_t cap8 = static_cast<int64_t>(num_sms()) * 8;  // persistent: 8 CTAs of 256 threads per SM
+  if (cols <= 256 * 32) {
+    // the row fits the registers of G threads (32 elements each): read x once
+    const int g = cols <= 4 * 32 ? 4 : cols <= 16 * 32 ? 16 : cols <= 64 * 32 ? 64 : 256;
+    const int64_t groups_r = (rows + 256 / g - 1) / (256 / g);
+    const unsigned grid_r = static_cast<unsigned>(groups_r < cap8 ? groups_r : cap8);
+    switch (g) {
+      case 4: quant_rowwise_reg_kernel<T, QKIND, 4><<<grid_r, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); break;
+      case 16: quant_rowwise_reg_kernel<T, QKIND, 16><<<grid_r, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); break;
+      case 64: quant_rowwise_reg_kernel<T, QKIND, 64><<<grid_r, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); break;
+      default: quant_rowwise_reg_kernel<T, QKIND, 256><<<grid_r, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); break;
+    }
+    GNK_LAUNCH_OK();
+    return GNK_OK;
+  }
+  const int lpr = 32;  // longer rows: two passes, the second one from L1/L2
   const int64_t rows_per_cta = 256 / lpr;
   const int64_t groups = (rows + rows_per_cta - 1) / rows_per_cta;
   const int64_t cap = static_cast<int64_t>(num_sms()) * 8;  // persistent: 8 CTAs of 256 threads per SM
@@ -443,7 +468,7 @@ static int launch_rowwise(const T* x, int64_t rows, int64_t cols, int64_t ldx, u
     quant_rowwise_kernel<T, QKIND, L><<<grid, 256, 0, st>>>(x, rows, cols, ldx, q, scale, perm_h, perm_l); \
     break;
   switch (lpr) {
-    GNK_RW(1) GNK_RW(2) GNK_RW(4) GNK_RW(8) GNK_RW(16) GNK_RW(32)
+    GNK_RW(32)
   }
 #undef GNK_RW
   GNK_LAUNCH_OK();
@@ -482,11 +507,12 @@ extern "C" int gnk_quant_mx(const void* x, int dtype, int64_t M, int64_t K, int6
   const int64_t nblk = (rows_out * ks_out + 255) / 256;
   if (nblk > 0x7FFFFFFF / 256) return GNK_ERR_TOO_LARGE;
   const unsigned grid = static_cast<unsigned>(nblk);
+  const int ks_shift = pow2_shift(ks_out);
   return dispatch_dtype(dtype, [&](auto* tag) -> int {
     using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
     const T* xp = static_cast<const T*>(x);
     uint8_t* qp = static_cast<uint8_t*>(q);
-#define GNK_MXK(QK, RL) quant_mx_kernel<T, QK, RL><<<grid, 256, 0, st>>>(xp, M, K, ldx, qp, sf, sf_swizzled, rows_out, ks_out)
+#define GNK_MXK(QK, RL) quant_mx_kernel<T, QK, RL><<<grid, 256, 0, st>>>(xp, M, K, ldx, qp, sf, sf_swizzled, rows_out, ks_out, ks_shift)
     if (rule == GNK_MX_OCP) {
       if (qkind == GNK_Q_E4M3) GNK_MXK(GNK_Q_E4M3, GNK_MX_OCP);
       else if (qkind == GNK_Q_E5M2) GNK_MXK(GNK_Q_E5M2, GNK_MX_OCP);
@@ -515,10 +541,11 @@ extern "C" int gnk_quant_nvfp4(const void* x, int dtype, int64_t M, int64_t K, i
   const int64_t nblk = (rows_out * ks_out + 255) / 256;
   if (nblk > 0x7FFFFFFF / 256) return GNK_ERR_TOO_LARGE;
   const unsigned grid = static_cast<unsigned>(nblk);
+  const int ks_shift = pow2_shift(ks_out);
   return dispatch_dtype(dtype, [&](auto* tag) -> int {
     using T = std::remove_cv_t<std::remove_pointer_t<decltype(tag)>>;
     quant_nvfp4_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), M, K, ldx, tensor_scale, eps,
-                                                 static_cast<uint8_t*>(q), sf, sf_swizzled, rows_out, ks_out);
+                                                 static_cast<uint8_t*>(q), sf, sf_swizzled, rows_out, ks_out, ks_shift);
     GNK_LAUNCH_OK();
     return (int)GNK_OK;
   });

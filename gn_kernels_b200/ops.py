@@ -222,6 +222,23 @@ def _(A, Bt):
     return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)
 
 
+@torch.library.custom_op("gnk::mm_f16", mutates_args=())
+def mm_f16(A: Tensor, Bt: Tensor, acc_f16: bool) -> Tensor:
+    _need_cuda(A, Bt)
+    M, K = A.shape
+    N = Bt.shape[0]
+    A, Bt, K = _prep_ab(A, Bt, 8)
+    C = torch.empty((M, N), dtype=torch.float16, device=A.device)
+    with torch.cuda.device(A.device):
+        check(lib().gnk_mm_f16(_p(A), A.stride(0), _p(Bt), Bt.stride(0), _p(C), N, M, N, K, int(acc_f16), _stream(A)), "gnk_mm_f16")
+    return C
+
+
+@mm_f16.register_fake
+def _(A, Bt, acc_f16):
+    return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.float16)
+
+
 @torch.library.custom_op("gnk::mm_i8", mutates_args=())
 def mm_i8(A: Tensor, Bt: Tensor, scale_A: Tensor | None, scale_B: Tensor | None, bias: Tensor | None, out_i32: bool) -> Tensor:
     _need_cuda(A, Bt)
@@ -316,6 +333,62 @@ def mm_nvfp4(A: Tensor, Bt: Tensor, SFA: Tensor, SFB: Tensor, alpha: float) -> T
 @mm_nvfp4.register_fake
 def _(A, Bt, SFA, SFB, alpha):
     return A.new_empty((A.shape[0], Bt.shape[0]), dtype=torch.bfloat16)
+
+
+def _gated_common(X, SFX, W1, SFW1, W3, SFW3):
+    _need_cuda(X, SFX, W1, SFW1, W3, SFW3)
+    M, Kh = X.shape
+    K = Kh * 2
+    N = W1.shape[0]
+    if N % 128 != 0 or K % 32 != 0:
+        raise ValueError(f"gated NVFP4 GEMM needs N % 128 == 0 and K % 32 == 0 (got N={N}, K={K})")
+    X, W1, W3 = _k_major(X), _k_major(W1), _k_major(W3)
+    SFX, SFW1, SFW3 = SFX.contiguous(), SFW1.contiguous(), SFW3.contiguous()
+    need_x = _ceil(M, 128) * _ceil(K // 16, 4)
+    need_w = _ceil(N, 128) * _ceil(K // 16, 4)
+    if SFX.numel() < need_x or SFW1.numel() < need_w or SFW3.numel() < need_w:
+        raise ValueError(f"swizzled scale buffers too small: need {need_x} / {need_w} bytes")
+    return X, SFX, W1, SFW1, W3, SFW3, M, N, K
+
+
+@torch.library.custom_op("gnk::gated_mm_nvfp4", mutates_args=())
+def gated_mm_nvfp4(X: Tensor, SFX: Tensor, ts_x: Tensor, W1: Tensor, SFW1: Tensor, ts_w1: Tensor, W3: Tensor, SFW3: Tensor,
+                   ts_w3: Tensor) -> Tensor:
+    X, SFX, W1, SFW1, W3, SFW3, M, N, K = _gated_common(X, SFX, W1, SFW1, W3, SFW3)
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=X.device)
+    with torch.cuda.device(X.device):
+        check(
+            lib().gnk_gated_mm_nvfp4(_p(X), X.stride(0), _p(SFX), _p(ts_x), _p(W1), _p(SFW1), _p(ts_w1), _p(W3), _p(SFW3), _p(ts_w3),
+                                     W1.stride(0), None, _p(C), N, None, M, N, K, _stream(X)),
+            "gnk_gated_mm_nvfp4",
+        )
+    return C
+
+
+@gated_mm_nvfp4.register_fake
+def _(X, SFX, ts_x, W1, SFW1, ts_w1, W3, SFW3, ts_w3):
+    return X.new_empty((X.shape[0], W1.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("gnk::gated_mm_nvfp4_quant", mutates_args=())
+def gated_mm_nvfp4_quant(X: Tensor, SFX: Tensor, ts_x: Tensor, W1: Tensor, SFW1: Tensor, ts_w1: Tensor, W3: Tensor, SFW3: Tensor,
+                         ts_w3: Tensor, ts_out: Tensor) -> tuple[Tensor, Tensor]:
+    X, SFX, W1, SFW1, W3, SFW3, M, N, K = _gated_common(X, SFX, W1, SFW1, W3, SFW3)
+    C = torch.empty((M, N // 2), dtype=torch.uint8, device=X.device)
+    SFC = torch.zeros((_ceil(M, 128), _ceil(N // 16, 4)), dtype=torch.uint8, device=X.device)  # padding rows stay 0
+    with torch.cuda.device(X.device):
+        check(
+            lib().gnk_gated_mm_nvfp4(_p(X), X.stride(0), _p(SFX), _p(ts_x), _p(W1), _p(SFW1), _p(ts_w1), _p(W3), _p(SFW3), _p(ts_w3),
+                                     W1.stride(0), _p(ts_out), _p(C), N // 2, _p(SFC), M, N, K, _stream(X)),
+            "gnk_gated_mm_nvfp4",
+        )
+    return C, SFC
+
+
+@gated_mm_nvfp4_quant.register_fake
+def _(X, SFX, ts_x, W1, SFW1, ts_w1, W3, SFW3, ts_w3, ts_out):
+    M, N = X.shape[0], W1.shape[0]
+    return X.new_empty((M, N // 2), dtype=torch.uint8), X.new_empty((_ceil(M, 128), _ceil(N // 16, 4)), dtype=torch.uint8)
 
 
 # ------------------------------------------------------------------ attention

@@ -129,6 +129,13 @@ int gnk_dequant_block(const void* q, const uint8_t* sf, int64_t M, int64_t K, in
 int gnk_mm_bf16(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc,
                 int64_t M, int64_t N, int64_t K, gnk_stream_t stream);
 
+/* C[M,N] fp16 = A[M,K] fp16 * Bt[N,K]^T; acc_f16 = 0: fp32 accumulate, != 0: the tensor core's fp16
+ * accumulator (kind::f16 with an F16 destination).  K % 8 == 0.
+ * Replaces: gn_kernels/triton_mm.py:128-171 `triton_mm` for float16 inputs, `acc_dtype=torch.float16`
+ * (:164-165) included. */
+int gnk_mm_f16(const void* A, int64_t lda, const void* Bt, int64_t ldb, void* C, int64_t ldc,
+               int64_t M, int64_t N, int64_t K, int acc_f16, gnk_stream_t stream);
+
 /* INT8 x INT8 -> exact INT32 accumulate.  out_kind GNK_OUT_I32: C int32 = acc (scales and
  * bias must be NULL).  GNK_OUT_BF16: C = bf16(f32(acc) * scale_A[m] * scale_B[n] + bias[n])
  * evaluated in that order in fp32; any of scale_A / scale_B / bias may be NULL.
@@ -159,6 +166,23 @@ int gnk_mm_mxfp8(const void* A, int64_t lda, const void* Bt, int64_t ldb, const 
 int gnk_mm_nvfp4(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA,
                  const uint8_t* SFB, float alpha, void* C, int64_t ldc, int64_t M, int64_t N,
                  int64_t K, gnk_stream_t stream);
+
+/* SwiGLU-gated dual NVFP4 GEMM:  out[M,N] = silu(o1) * o3,  o1 = (X W1^T) * (ts_w1 * ts_x),
+ * o3 = (X W3^T) * (ts_w3 * ts_x), evaluated in fp32 as (o1 * o3) * sigmoid(o1).  X [M, K/2], W1 / W3
+ * [N, K/2] packed E2M1 (ld in bytes), SFX / SFW1 / SFW3 E4M3 block scales in the swizzled layout, ts_*
+ * fp32 per-tensor scales in DEVICE memory.  One tcgen05 tile holds 128 rows of W1 and the same 128
+ * rows of W3, so X is read once for both products.
+ *   ts_out == NULL: C is bf16 [M, N] (ldc in elements), SFC must be NULL.
+ *   ts_out != NULL: the bf16 result is quantised to NVFP4 with per-tensor scale ts_out[0] in the
+ *     epilogue: C = packed E2M1 [M, N/2] (ldc in bytes), SFC = E4M3 scales, swizzled layout
+ *     [ceil128(M), N/16]; rows >= M of SFC are not written.  Bytes and scales equal
+ *     gnk_quant_nvfp4 applied to the bf16 output of the ts_out == NULL call.
+ * N % 128 == 0, K % 32 == 0.
+ * Replaces: gn_kernels/cutedsl/sm120/sm120_gated_gemm_nvfp4.py:513-555 `mm` (epilogue :374-464). */
+int gnk_gated_mm_nvfp4(const void* X, int64_t ldx, const uint8_t* SFX, const float* ts_x, const void* W1,
+                       const uint8_t* SFW1, const float* ts_w1, const void* W3, const uint8_t* SFW3,
+                       const float* ts_w3, int64_t ldw, const float* ts_out, void* C, int64_t ldc, uint8_t* SFC,
+                       int64_t M, int64_t N, int64_t K, gnk_stream_t stream);
 
 /* FP8 with DeepSeek-style scales: SFA fp32 [M, K/128] stored M-major (element (m,kb) at
  * SFA[kb*ld_sfa + m]), SFB fp32 [N/128, K/128] row-major (ld_sfb).  Each 128-deep partial

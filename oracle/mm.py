@@ -8,6 +8,7 @@
                                         gn_kernels/cutedsl/sm100/sm100_mm_nvfp4.py:383-386
 * per-tensor NVFP4 alpha                gn_kernels/cutedsl/sm120/sm120_gated_gemm_nvfp4.py:317-319
 * FP8 1x128 / 128x128 block scaling     gn_kernels/cutedsl/sm120/sm120_mm_fp8_1d2d.py:166-224
+* SwiGLU-gated dual NVFP4 GEMM          gn_kernels/cutedsl/sm120/sm120_gated_gemm_nvfp4.py:317-319,398-404,513-555
 * bf16 mm                               gn_kernels/cutedsl/sm100/sm100_mm_bf16.py:252-255
 
 Convention everywhere: A is [M, K] K-contiguous; "Bt" is the [N, K] K-contiguous buffer
@@ -96,6 +97,22 @@ def mm_nvfp4(A_packed, Bt_packed, sfa_codes, sfb_codes, alpha: float = 1.0):
     A = torch.from_numpy(quant.dequantize_nvfp4(np.asarray(A_packed), np.asarray(sfa_codes), 1.0))
     Bt = torch.from_numpy(quant.dequantize_nvfp4(np.asarray(Bt_packed), np.asarray(sfb_codes), 1.0))
     return ((A @ Bt.T) * np.float32(alpha)).bfloat16()
+
+
+def gated_mm_nvfp4(X_packed, sfx_codes, ts_x, W1_packed, sfw1_codes, ts_w1, W3_packed, sfw3_codes, ts_w3):
+    """SwiGLU-gated dual NVFP4 GEMM, gn_kernels/cutedsl/sm120/sm120_gated_gemm_nvfp4.py:513-555 with
+    the epilogue arithmetic of :317-319 and :398-404, in fp32:
+        o1 = (X W1^T) * (ts_w1 * ts_x);  o3 = (X W3^T) * (ts_w3 * ts_x);  out = bf16((o1 * o3) * sigmoid(o1))
+    (tests/test_sm120_gated_gemm_nvfp4.py:43-44 states the same as silu(mm1) * mm3).  Packed operands
+    and row-major E4M3 block scales as in mm_nvfp4."""
+    X = torch.from_numpy(quant.dequantize_nvfp4(np.asarray(X_packed), np.asarray(sfx_codes), 1.0))
+    W1 = torch.from_numpy(quant.dequantize_nvfp4(np.asarray(W1_packed), np.asarray(sfw1_codes), 1.0))
+    W3 = torch.from_numpy(quant.dequantize_nvfp4(np.asarray(W3_packed), np.asarray(sfw3_codes), 1.0))
+    a1 = np.float32(ts_w1) * np.float32(ts_x)
+    a3 = np.float32(ts_w3) * np.float32(ts_x)
+    o1 = (X @ W1.T) * a1
+    o3 = (X @ W3.T) * a3
+    return ((o1 * o3) * torch.sigmoid(o1)).bfloat16()
 
 
 def mm_f8_block128(A_codes, sfa, Bt_codes, sfb, bias=None, add=None):

@@ -212,10 +212,11 @@ def test_varlen_packed_sequences(gk, dt, causal, lens):
     assert out.shape == q.shape and out.dtype == dt
     ref = torch.cat([oattn.attention_f32(a[None], b[None], c[None], causal=causal)[0] for a, b, c in zip(qs, ks, vs)]).to(dt)
     assert_attn(out, ref)
-    # the batched kernel on each sequence alone gives the same bits (same tiles, same order)
+    # the batched kernel on each sequence alone agrees (same tiles; only the per-warp decision when to
+    # rescale O can differ, because a warp's spare rows hold the next sequence's queries here)
     for i, (a, b, c) in enumerate(zip(qs, ks, vs)):
         one = gk.triton_attn(a[None].cuda(), b[None].cuda(), c[None].cuda(), causal=causal)[0]
-        assert torch.equal(one, out[int(qo[i]) : int(qo[i + 1])])
+        assert_parity(out[int(qo[i]) : int(qo[i + 1])], one, tol=4e-3, atol_frac=2e-3)
 
 
 def test_varlen_fp16_accumulation(gk):

@@ -86,6 +86,37 @@ def test_int8_exact(gk, tile, M, N, K):
     assert torch.equal(out.cpu(), omm.mm_i8_row_scaled(A, Bt, None, sB))
 
 
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("acc16", [False, True])
+def test_fp16_and_fp16_accumulate(gk, tile, M, N, K, acc16):
+    """fp16 operands (upstream triton_mm.py:155-161: output takes A's dtype) with fp32 accumulation, and
+    `acc_dtype=torch.float16` (:164-165).  The fp16-accumulated result is compared with the emulation
+    upstream uses for that mode (tests/test_cuda_mm.py:66-75: fp32 products of one MMA K step added into
+    an fp16 sum) and, loosely, with the fp32 result: the tensor core may keep more bits inside an
+    instruction than the emulation does, never fewer."""
+    K = max(K, 8) // 8 * 8
+    force(tile)
+    g = torch.Generator().manual_seed(M + 3 * N + K)
+    A = (torch.randn(M, K, generator=g) / K**0.25).half()
+    Bt = (torch.randn(N, K, generator=g) / K**0.25).half()
+    out = gk.triton_mm(A.cuda(), Bt.cuda().T, acc_dtype=torch.float16 if acc16 else None)
+    assert out.dtype == torch.float16
+    exact = A.float() @ Bt.float().T
+    if not acc16:
+        assert_parity(out, exact.half())
+        return
+    emu = torch.zeros(M, N, dtype=torch.float16)
+    for k0 in range(0, K, 16):  # one kind::f16 instruction covers 16 elements of K
+        emu = (emu.float() + A[:, k0 : k0 + 16].float() @ Bt[:, k0 : k0 + 16].float().T).half()
+    scale = float(exact.abs().max())
+    err_emu = float((out.float().cpu() - emu.float()).abs().max()) / scale
+    err_exact = float((out.float().cpu() - exact).abs().max()) / scale
+    emu_exact = float((emu.float() - exact).abs().max()) / scale
+    assert err_exact <= max(2.0 * emu_exact, 2e-3), (err_exact, emu_exact)
+    assert err_emu <= max(2.0 * emu_exact, 2e-3), (err_emu, emu_exact)
+
+
 def test_int8_golden_and_config1(gk, golden_mm):
     g = golden_mm
     A, Bt = torch.from_numpy(g["i8_A"]), torch.from_numpy(g["i8_Bt"])
@@ -308,7 +339,9 @@ def test_bad_arguments(gk):
     with pytest.raises(AssertionError):
         gk.triton_mm(A, torch.zeros(16, 32, dtype=torch.int8, device="cuda"))
     with pytest.raises(NotImplementedError):
-        gk.triton_mm(A.half(), A.half().T)
+        gk.triton_mm(A.float(), A.float().T)
+    with pytest.raises(NotImplementedError):  # the fp16 accumulator goes with fp16 operands
+        gk.triton_mm(A.bfloat16(), A.bfloat16().T, acc_dtype=torch.float16)
     with pytest.raises(RuntimeError):
         gk.triton_mm(A.cpu(), A.cpu().T)
 
