@@ -80,9 +80,15 @@ EXTRA_WORKLOADS = [
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the
 # one-kernel ncu captures summarised under profiles/ (file named beside each figure)
 NCU_TRAFFIC = {
-    "mxfp8_gemm_8192": (356.7e6 + 117.0e6, "profiles/gemm_mxfp8_8192_2cta.md"),
-    "attn_fp8_causal": (120.2e6 + 88.1e6, "profiles/attn_fwd_fp8_causal_b4_l4096.md"),
-    "nvfp4_quant_8192": (134.2e6 + 20.4e6, "profiles/quant_nvfp4_8192x8192.md"),
+    "bf16_gemm_rs": (6486.4e6 + 132.4e6, "profiles/ncu_counters_by_kernel.md (N = 1: the plain GEMM)"),
+    "mxfp8_gemm_8192": (354.8e6 + 116.8e6, "profiles/ncu_counters_by_kernel.md"),
+    "nvfp4_gemm_8192": (167.2e6 + 103.2e6, "profiles/ncu_counters_by_kernel.md"),
+    "fp8_block128_gemm_8192": (698.8e6 + 127.9e6, "profiles/ncu_counters_by_kernel.md"),
+    "mxfp8_gemm_m16": (69.4e6 + 0.7e6, "profiles/ncu_counters_by_kernel.md"),
+    "attn_fp8_causal": (120.3e6 + 86.4e6, "profiles/ncu_counters_by_kernel.md"),
+    "nvfp4_quant_8192": (134.2e6 + 20.2e6, "profiles/ncu_counters_by_kernel.md"),
+    "mxfp8_quant_8192": (134.2e6 + 39.8e6, "profiles/ncu_counters_by_kernel.md"),
+    "rowwise_quant_attn": (134.3e6 + 39.3e6, "profiles/ncu_counters_by_kernel.md"),
 }
 
 

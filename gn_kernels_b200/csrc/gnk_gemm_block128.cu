@@ -1,20 +1,31 @@
 // FP8 (E4M3) GEMM with DeepSeek-style scaling: one fp32 scale per row of A per 128 K elements
 // (SFA, stored M-major) and one per 128 x 128 block of B (SFB).  The tensor core cannot apply
 // fp32 scales, so every 128-deep partial product is formed on its own in TMEM (tcgen05
-// kind::f8f6f4, accumulate off at the block start) and promoted by the four epilogue warps:
-//   acc[m][n] += partial[m][n] * (SFA[m][kb] * SFB[n/128][kb])          (fp32 registers)
-// Two TMEM buffers alternate per K block so the MMA of block kb+1 overlaps the promotion of kb.
-// Persistent CTAs over 128 x 128 output tiles; warps 0-3 promote + store, warp 4 TMA producer,
-// warp 5 MMA issuer.  All barrier waits are bounded.
+// kind::f8f6f4, accumulate off at the block start) and promoted into fp32 registers:
+//   acc[m][n] += partial[m][n] * (SFA[m][kb] * SFB[n/128][kb])
+// The promotion, not the tensor core, sets the pace of such a kernel, so it gets most of the SM:
+//   warps 0-7  promotion + store.  Warp w owns rows 32 (w & 3) .. +31 of the 128-row tile and the 128-column
+//              half (w >> 2) of the 256-column tile: exactly one 128 x 128 scale block of B per warp, 128 fp32
+//              accumulators per thread (packed f32x2 FMAs, TMEM read 64 columns per instruction)
+//   warp 8     TMA producer (A 128 x 128, B 256 x 128 bytes per K block, 4 stages)
+//   warp 9     MMA issuer: four M = 128, N = 256, K = 32 MMAs per K block into one of two 256-column
+//              TMEM buffers, so the MMA of block kb + 1 overlaps the promotion of kb
+//   warps 10-11 idle: they complete the warpgroup that hands its registers to the promotion warps
+//              (setmaxnreg: 224 for warps 0-7, 56 for the rest)
+// Persistent CTAs over 128 x 256 output tiles.  All barrier waits are bounded.
 #include "gnk_common.cuh"
 
 namespace gnk {
 namespace {
 
-constexpr int kTile = 128;
-constexpr int kStageBytes = 2 * kTile * 128;  // A and B tiles of one 128-element K block
-constexpr int kStages = 6;
+constexpr int kTileM = 128, kTileN = 256;
+constexpr int kABytes = kTileM * 128, kBBytes = kTileN * 128;
+constexpr int kStageBytes = kABytes + kBBytes;  // A and B tiles of one 128-element K block
+constexpr int kStages = 4;
 constexpr int kSmem = kStages * kStageBytes + 2048;
+constexpr int kThreads = 384;
+constexpr int kPromoteRegs = 224, kRoleRegs = 56;
+static_assert(2 * kPromoteRegs + kRoleRegs <= 3 * 168, "register split exceeds the launch allocation");
 
 struct Blk128Args {
   int M, N, k_blocks, tiles_m, tiles_n;
@@ -30,13 +41,13 @@ struct Blk128Args {
   int vec_ok;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
     gemm_block128_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const Blk128Args g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   auto stage_a = [&](int s) { return base + s * kStageBytes; };
-  auto stage_b = [&](int s) { return base + s * kStageBytes + kTile * 128; };
+  auto stage_b = [&](int s) { return base + s * kStageBytes + kABytes; };
   const uint32_t bars = base + kStages * kStageBytes;
   auto bar_full = [&](int s) { return bars + 8 * s; };
   auto bar_empty = [&](int s) { return bars + 8 * (kStages + s); };
@@ -53,16 +64,16 @@ __global__ void __launch_bounds__(192, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull(s), 1);
-      mbar_init(bar_tempty(s), 4);
+      mbar_init(bar_tempty(s), 8);  // one arrival per promotion warp
     }
     fence_mbar_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
   }
-  if (warp == 5) {
-    tmem_alloc<1>(tmem_slot, 256);
+  if (warp == 9) {
+    tmem_alloc<1>(tmem_slot, 512);
     tmem_relinquish<1>();
   }
   tc_fence_before();
@@ -71,90 +82,112 @@ __global__ void __launch_bounds__(192, 1)
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  if (warp == 4) {
-    const bool leader = elect_one();
-    uint32_t stage = 0, parity = 1;
-    bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int tm = t % g.tiles_m, tn = t / g.tiles_m;
-      for (int kb = 0; kb < g.k_blocks; ++kb) {
-        if (!mbar_wait(bar_empty(stage), parity, (0x21u << 24) | (1u << 16) | stage)) { ok = false; break; }
-        if (leader) {
-          mbar_expect_tx(bar_full(stage), kStageBytes);
-          tma_load_2d(stage_a(stage), &tm_a, bar_full(stage), kb * 128, tm * kTile);
-          tma_load_2d(stage_b(stage), &tm_b, bar_full(stage), kb * 128, tn * kTile);
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRoleRegs));
+    if (warp == 8) {
+      const bool leader = elect_one();
+      uint32_t stage = 0, parity = 1;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int tm = t % g.tiles_m, tn = t / g.tiles_m;
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty(stage), parity, (0x21u << 24) | (1u << 16) | stage)) { ok = false; break; }
+          if (leader) {
+            mbar_expect_tx(bar_full(stage), kStageBytes);
+            tma_load_2d(stage_a(stage), &tm_a, bar_full(stage), kb * 128, tm * kTileM);
+            tma_load_2d(stage_b(stage), &tm_b, bar_full(stage), kb * 128, tn * kTileN);  // rows beyond N read as zero
+          }
+          __syncwarp();
+          if (++stage == kStages) { stage = 0; parity ^= 1; }
         }
-        __syncwarp();
-        if (++stage == kStages) { stage = 0; parity ^= 1; }
       }
-    }
-  } else if (warp == 5) {
-    const bool leader = elect_one();
-    constexpr uint32_t kIdesc = idesc_dense(1, 0, 0, kTile, kTile);
-    uint32_t stage = 0, parity = 0, it = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
-        const uint32_t buf = it & 1;
-        if (!mbar_wait(bar_tempty(buf), ((it >> 1) & 1) ^ 1, (0x22u << 24) | (2u << 16))) { ok = false; break; }
-        if (!mbar_wait(bar_full(stage), parity, (0x22u << 24) | (3u << 16) | stage)) { ok = false; break; }
-        tc_fence_after();
-        const uint64_t a_desc = sdesc_k128(stage_a(stage));
-        const uint64_t b_desc = sdesc_k128(stage_b(stage));
-        const uint32_t d = tmem_base + buf * kTile;
-        if (leader) {
+    } else if (warp == 9) {
+      const bool leader = elect_one();
+      constexpr uint32_t kIdesc = idesc_dense(1, 0, 0, kTileM, kTileN);
+      uint32_t stage = 0, parity = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t buf = it & 1;
+          if (!mbar_wait(bar_tempty(buf), ((it >> 1) & 1) ^ 1, (0x22u << 24) | (2u << 16))) { ok = false; break; }
+          if (!mbar_wait(bar_full(stage), parity, (0x22u << 24) | (3u << 16) | stage)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t a_desc = sdesc_k128(stage_a(stage));
+          const uint64_t b_desc = sdesc_k128(stage_b(stage));
+          const uint32_t d = tmem_base + buf * kTileN;
+          if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma<MmaKind::F8F6F4, 1>(d, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, kk != 0);
-          tc_commit<1>(bar_empty(stage));
-          tc_commit<1>(bar_tfull(buf));
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma<MmaKind::F8F6F4, 1>(d, a_desc + 2 * kk, b_desc + 2 * kk, kIdesc, kk != 0);
+            tc_commit<1>(bar_empty(stage));
+            tc_commit<1>(bar_tfull(buf));
+          }
+          __syncwarp();
+          if (++stage == kStages) { stage = 0; parity ^= 1; }
         }
-        __syncwarp();
-        if (++stage == kStages) { stage = 0; parity ^= 1; }
       }
     }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kPromoteRegs));
+    const int quad = warp & 3, half = warp >> 2;
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int tm = t % g.tiles_m, tn = t / g.tiles_m;
-      const int row = tm * kTile + warp * 32 + lane;
+      const int row = tm * kTileM + quad * 32 + lane;
       const int rowc = min(row, g.M - 1);
-      float acc[kTile];
+      const int col0 = tn * kTileN + half * 128;  // this warp's 128 columns = one scale block of B
+      const int nb = min(col0 / 128, g.N / 128 - 1);
+      uint64_t acc[64];  // 128 fp32 accumulators as packed pairs
 #pragma unroll
-      for (int i = 0; i < kTile; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 64; ++i) acc[i] = 0ull;
+      // scales are fetched one K block ahead: their global-memory latency would otherwise sit in front
+      // of every promotion
+      const float* sfa_p = g.sfa + rowc;
+      const float* sfb_p = g.sfb + nb * g.ld_sfb;
+      float sa_next = __ldg(sfa_p), sb_next = __ldg(sfb_p);
       for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
         const uint32_t buf = it & 1;
-        const float sf = __fmul_rn(__ldg(g.sfa + kb * g.ld_sfa + rowc), __ldg(g.sfb + tn * g.ld_sfb + kb));
+        const float sf = __fmul_rn(sa_next, sb_next);
+        if (kb + 1 < g.k_blocks) {
+          sa_next = __ldg(sfa_p + (kb + 1) * g.ld_sfa);
+          sb_next = __ldg(sfb_p + kb + 1);
+        }
+        const uint64_t sf2 = f2_pack(sf, sf);
         if (!mbar_wait(bar_tfull(buf), (it >> 1) & 1, (0x23u << 24) | (4u << 16))) { ok = false; break; }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * kTile;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kTileN + half * 128;
+        // two 64-column reads per K block: the TMEM round trip (a few hundred cycles) is what a promotion
+        // warp waits for, so fewer, wider reads beat more, overlapped ones
+        uint32_t r[64];
+        auto accumulate = [&](int c) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c * 32, r);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sf, acc[c * 32 + i]);
-        }
+          for (int i = 0; i < 64; i += 2)
+            acc[c * 32 + (i >> 1)] = f2_fma(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sf2, acc[c * 32 + (i >> 1)]);
+        };
+        tmem_ld64(taddr, r);
+        tc_wait_ld();
+        accumulate(0);
+        tmem_ld64(taddr + 64, r);
+        tc_wait_ld();
+        // every column of the buffer has been read: hand it back before the last half is accumulated
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty(buf));
+        accumulate(1);
       }
-      if (!ok || row >= g.M) continue;
-      const int col0 = tn * kTile;
+      if (!ok || row >= g.M || col0 >= g.N) continue;
       __nv_bfloat16* crow = g.C + static_cast<int64_t>(row) * g.ldc + col0;
-      const __nv_bfloat16* arow = g.add ? g.add + static_cast<int64_t>(row) * g.ld_add + col0 : nullptr;
 #pragma unroll
-      for (int i = 0; i < kTile; i += 8) {
+      for (int i = 0; i < 128; i += 8) {
         float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) f2_unpack(acc[(i + e) >> 1], f[e], f[e + 1]);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int c = min(col0 + i + e, g.N - 1);
-          float v = acc[i + e];
-          if (arow) v += __bfloat162float(g.add[static_cast<int64_t>(row) * g.ld_add + c]);
-          if (g.bias) v += __bfloat162float(g.bias[c]);
-          f[e] = v;
+          if (g.add) f[e] += __bfloat162float(g.add[static_cast<int64_t>(row) * g.ld_add + c]);
+          if (g.bias) f[e] += __bfloat162float(g.bias[c]);
         }
         if (g.vec_ok && col0 + i + 8 <= g.N) {
           *reinterpret_cast<uint4*>(crow + i) =
@@ -167,9 +200,9 @@ __global__ void __launch_bounds__(192, 1)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, 256);
+    tmem_dealloc<1>(tmem_base, 512);
   }
 }
 
@@ -191,16 +224,16 @@ extern "C" int gnk_mm_f8_block128(const void* A, int64_t lda, const float* SFA, 
   int rc = check_arch();
   if (rc != GNK_OK) return rc;
   CUtensorMap tm_a, tm_b;
-  rc = make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, M, K, lda, kTile, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, M, K, lda, kTileM, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
-  rc = make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, Bt, N, K, ldb, kTile, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, Bt, N, K, ldb, kTileN, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
   Blk128Args g{};
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.k_blocks = static_cast<int>(K / 128);
-  g.tiles_m = static_cast<int>((M + kTile - 1) / kTile);
-  g.tiles_n = static_cast<int>(N / kTile);
+  g.tiles_m = static_cast<int>((M + kTileM - 1) / kTileM);
+  g.tiles_n = static_cast<int>((N + kTileN - 1) / kTileN);
   g.sfa = SFA;
   g.ld_sfa = ld_sfa;
   g.sfb = SFB;
@@ -215,7 +248,7 @@ extern "C" int gnk_mm_f8_block128(const void* A, int64_t lda, const float* SFA, 
   int grid = num_sms();
   const int tiles = g.tiles_m * g.tiles_n;
   if (grid > tiles) grid = tiles;
-  gemm_block128_kernel<<<grid, 192, kSmem, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, g);
+  gemm_block128_kernel<<<grid, kThreads, kSmem, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, g);
   GNK_LAUNCH_OK();
   return GNK_OK;
 }

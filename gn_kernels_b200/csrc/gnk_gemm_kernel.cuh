@@ -474,6 +474,23 @@ __device__ __forceinline__ void gated_epilogue(uint32_t taddr_row, uint32_t acc,
   }
 }
 
+// The same staging for 16 accumulator columns that are already in registers.
+template <MmaKind KIND, int EPI>
+__device__ __forceinline__ void stage_cols16_sw128(const uint32_t (&raw)[16], int c, const GemmArgs& g, int ncol0, float sa,
+                                                   uint32_t stg, int r) {
+  float f[16];
+  finish_cols<KIND, EPI, 16>(raw, g, ncol0 + c, sa, f);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int piece = (c >> 3) + j;
+    const uint32_t addr = stg + (piece >> 3) * 4096 + r * 128 + (((piece & 7) ^ (r & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_out<KIND, EPI>(g, f[8 * j], f[8 * j + 1])),
+                 "r"(pack_out<KIND, EPI>(g, f[8 * j + 2], f[8 * j + 3])), "r"(pack_out<KIND, EPI>(g, f[8 * j + 4], f[8 * j + 5])),
+                 "r"(pack_out<KIND, EPI>(g, f[8 * j + 6], f[8 * j + 7]))
+                 : "memory");
+  }
+}
+
 template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1>
 __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -786,10 +803,20 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
           if (C::kOverlap && i == 0) {
             const int o0 = acc == 0 ? C::kAccStride : 0;
             const int o1 = o0 + C::kOverlapCols;
-            drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, o0, o1, g, ncol0, sa, buf - cb * 4096, lane);
+            // The MMA warp cannot start the next tile before these columns are free, so they are pulled
+            // into registers in one go (all loads in flight, one wait) and released at once; converting
+            // and staging them happens afterwards.
+            constexpr int kShared16 = C::kOverlapCols / 16;
+            uint32_t shared_raw[kShared16 > 0 ? kShared16 : 1][16];
+#pragma unroll
+            for (int q = 0; q < kShared16; ++q) tmem_ld16(taddr_row + o0 + q * 16, shared_raw[q]);
+            tc_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(partial);
+#pragma unroll
+            for (int q = 0; q < kShared16; ++q)
+              stage_cols16_sw128<KIND, EPI>(shared_raw[q], o0 + q * 16, g, ncol0, sa, buf - cb * 4096, lane);
             if (acc == 0) drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, 192, o0, g, ncol0, sa, buf - cb * 4096, lane);
             else drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, o1, 64, g, ncol0, sa, buf - cb * 4096, lane);
           } else {
