@@ -20,6 +20,12 @@
 //   warp 9     producer: TMA loads of both Q tiles (once), K and V tiles (rings of kStages)
 //   warps 10-11 idle (they complete the warpgroup whose registers are handed to the softmax warps)
 // TMEM: S_A / P_A [0,128) S_B / P_B [128,256) O_A [256,384) O_B [384,512).
+// A variant with 64-key score sub-tiles (two score buffers per query tile, Q K^T two sub-tiles ahead of
+// the softmax so that the chain softmax -> P V -> Q K^T -> softmax no longer contains the tensor core)
+// was built and measured: correct, but slower (771 / 928 against 868 / 1069 TFLOP/s causal / full):
+// the softmax is bound by dependent-issue latency (ncu: 9 instructions per score element, 0.42 issued
+// per scheduler cycle with two softmax warps per scheduler, stall reason "wait"), and halving the step
+// doubles its fixed costs (TMEM round trips, barrier hand-shakes, votes) without removing instructions.
 // Every barrier wait is bounded (see mbar_wait); a softmax warp whose wait runs out stops waiting
 // but keeps arriving at the barriers of its group, so the CTA always reaches its end.
 #pragma once
@@ -397,7 +403,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_wait_ld();
       // from here on the score region may be overwritten with P
       float x[4][32];
-      float xmax = -INFINITY;
+      // independent partial maxima / sums per 32-column chunk: one serial chain over the whole row
+      // would cost ~4 cycles per link and is exactly what a latency-bound softmax thread cannot afford
+      float xm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       auto scale_and_max = [&](auto masked) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -418,11 +426,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               x[c][i] = v0;
               x[c][i + 1] = v1;
             }
-            xmax = max3(xmax, max3(x[c][i4 * 4], x[c][i4 * 4 + 1], x[c][i4 * 4 + 2]), x[c][i4 * 4 + 3]);
+            xm[c] = max3(xm[c], max3(x[c][i4 * 4], x[c][i4 * 4 + 1], x[c][i4 * 4 + 2]), x[c][i4 * 4 + 3]);
           }
         }
       };
       if (need_mask) scale_and_max(std::true_type{}); else scale_and_max(std::false_type{});
+      const float xmax = fmaxf(fmaxf(xm[0], xm[1]), fmaxf(xm[2], xm[3]));
       if (tr) tr[2] = clock64();
       // qs >= 0 (absmax scales), so max(qs * x) = qs * max(x); a fully masked row keeps the old maximum
       const float mt = fmaxf(m_used, xmax == -INFINITY ? -INFINITY : qs * xmax);
@@ -450,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       // ---- P = exp2(qs * x - max), row sum, 16-bit P back into TMEM ----
       if (tr) tr[3] = clock64();
-      uint64_t rs2 = f2_pack(0.f, 0.f);
+      uint64_t rs2[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
       const uint64_t qs2 = f2_pack(qs, qs), negm2 = f2_pack(-m_used, -m_used);
 #pragma unroll
       for (int c2 = 0; c2 < 2; ++c2) {
@@ -471,14 +480,14 @@ __global__ void __launch_bounds__(kThreads, 1)
               p0 = fast_exp2(t0);
               p1 = fast_exp2(t1);
             }
-            rs2 = f2_add(rs2, f2_pack(p0, p1));
+            rs2[c] = f2_add(rs2[c], f2_pack(p0, p1));
             pk[cc * 16 + (i >> 1)] = pack16x2<VT>(p0, p1);
           }
         }
         tmem_st32(tm_s + c2 * 32, pk);
       }
       float rs0, rs1;
-      f2_unpack(rs2, rs0, rs1);
+      f2_unpack(f2_add(f2_add(rs2[0], rs2[1]), f2_add(rs2[2], rs2[3])), rs0, rs1);
       l += rs0 + rs1;
       tc_wait_st();
       if (tr) tr[4] = clock64();
