@@ -90,3 +90,46 @@ def test_missing_peer_times_out_once_and_context_survives(M, N, K, timeout_ms):
     torch.cuda.synchronize()
     assert max_rel_err(c, mm_bf16(a.cpu(), b.cpu())) <= 1e-2
     assert _lib.device_status(clear=True) == (0, 0)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (2048, 768, 512), (256, 384, 192)], ids=["pair-tile", "multi-tile", "128-tile"])
+def test_two_ranks_one_after_the_other_on_one_gpu(M, N, K):
+    """The whole reduce-scatter protocol (peer stores into the owner's slots, per-warp flag signals, reducers,
+    flag reset, exit barrier) checked against the oracle on ONE GPU, without two kernels ever waiting
+    for each other: the ranks of a world of 2 run one after the other.  The first rank to run pushes its
+    tiles and signals, finds nobody answering and gives up after a short timeout (its own output is
+    discarded); the second one then finds every signal it needs already there, reduces, and must end
+    cleanly with the right rows and its flag words back at zero."""
+    from gn_kernels_b200 import _lib
+    from oracle import gemm_rs as ors
+    from oracle.mm import max_rel_err
+
+    L = _lib.lib()
+    _lib.device_status(clear=True)
+    W = 2
+    g = torch.Generator().manual_seed(M + N + K)
+    xs = [(torch.randn(M, K, generator=g) / (K * W) ** 0.5).bfloat16().cuda() for _ in range(W)]
+    ws = [(torch.randn(N, K, generator=g) / (K * W) ** 0.5).bfloat16().cuda() for _ in range(W)]
+    refs = ors.gemm_rs([t.cpu() for t in xs], [t.cpu() for t in ws])
+    words = L.gnk_gemm_rs_flag_words(M, N, W)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(rank, staging, flags, out, timeout_ms):
+        sp = (ctypes.c_void_p * W)(*[t.data_ptr() for t in staging])
+        fp = (ctypes.c_void_p * W)(*[t.data_ptr() for t in flags])
+        return L.gnk_gemm_rs_bf16(_p(xs[rank]), K, _p(ws[rank]), K, sp, fp, _p(out), N, M, N, K, rank, W, timeout_ms, stream)
+
+    for second in range(W):  # the rank whose output is checked runs second
+        first = 1 - second
+        staging = [torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+        flags = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(W)]
+        scrap = torch.empty(M // W, N, dtype=torch.bfloat16, device="cuda")
+        out = torch.full((M // W, N), 7.0, dtype=torch.bfloat16, device="cuda")
+        assert call(first, staging, flags, scrap, 30) == 0
+        torch.cuda.synchronize()
+        assert _lib.device_status(clear=True)[0] == _lib.ERR_TIMEOUT  # nobody answered the first rank
+        assert call(second, staging, flags, out, 2000) == 0
+        torch.cuda.synchronize()
+        assert _lib.device_status(clear=True) == (0, 0)  # the second rank found everything it waited for
+        assert max_rel_err(out, refs[second]) <= 1e-2
+        assert int(flags[second].abs().sum()) == 0, "the rank that completed must leave its flag words at zero"
