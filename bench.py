@@ -608,19 +608,29 @@ class Runner:
         return int(max(1, min(20000, seconds * 1e3 / max(ms, 1e-3))))
 
     def timed(self, fn, steps: int, flush: bool):
-        """K launches, one event pair each.  Returns (ms of the whole region, per-launch ms list)."""
+        """K launches.  Returns (ms of the whole region, per-launch ms list).  With an L2 flush between
+        steps every launch has its own event pair (the flushes are not part of a step); otherwise ONE
+        pair brackets the K back-to-back launches and the per-launch time is their mean (an event
+        record between two launches keeps the second from starting as the first drains)."""
+        if not flush:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            self.barrier()
+            total = e0.elapsed_time(e1)
+            return total, [total / steps] * steps
         ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ev1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         for i in range(steps):
-            if flush:
-                self.flush()
+            self.flush()
             ev0[i].record()
             fn()
             ev1[i].record()
         self.barrier()
         per = [a.elapsed_time(b) for a, b in zip(ev0, ev1)]
-        total = float(np.sum(per)) if flush else ev0[0].elapsed_time(ev1[-1])  # L2 flushes between steps are not part of a step
-        return total, per
+        return float(np.sum(per)), per
 
     def measure(self, name: str, steps: int, warmup: int, main: bool) -> dict:
         from gn_kernels_b200 import _lib
@@ -662,6 +672,11 @@ class Runner:
         if clocks and clocks.get("sm_mhz"):
             # throughput follows the SM clock on this power-capped part: time x clock compares runs on different boxes
             rec["roofline"]["achieved_per_sm_mhz"] = rec["roofline"]["achieved"] / clocks["sm_mhz"]
+
+        # SM clock seen from inside the kernel: the same launches once more, back to back, with the
+        # library's trace hook on (cycle counter and wall clock at entry and exit of CTA 0)
+        if (w["family"] == "gemm" or (w["family"] == "rs" and self.world == 1)) and name != "fp8_block128_gemm_8192" and not flush:
+            rec["in_kernel"] = self.in_kernel_clock(step, max(steps, lead // 2))
 
         # local GEMM of the same shape without the exchange (reduce-scatter workload only), same run
         if "local_gemm" in w:
@@ -706,6 +721,29 @@ class Runner:
             del hp
         rec["_w"] = w
         return rec
+
+    def in_kernel_clock(self, step, n: int) -> dict:
+        """Cycles and nanoseconds CTA 0 of the last of `n` back-to-back launches (about as many as the
+        lead-in, so the clock has settled under load again) spent in the kernel."""
+        from gn_kernels_b200 import _lib
+
+        L = _lib.lib()
+        span_at = 2 * 2 * 256 * 3
+        buf = torch.zeros(span_at + 4, dtype=torch.int64, device=self.dev)
+        L.gnk_debug_trace(ctypes.c_void_p(buf.data_ptr()))
+        try:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                step()
+            e1.record()
+            torch.cuda.synchronize(self.dev)
+        finally:
+            L.gnk_debug_trace(None)
+        c0, t0, c1, t1 = (int(v) for v in buf[span_at:].tolist())
+        cycles, ns = c1 - c0, t1 - t0
+        return {"sm_cycles": cycles, "ns": ns, "sm_mhz": cycles / ns * 1e3 if ns > 0 else None, "event_ms_per_launch": e0.elapsed_time(e1) / n,
+                "what": "clock64 and globaltimer at entry and exit of CTA 0, last of the launches; globaltimer ticks in steps of up to 1 us"}
 
     def roofline(self, w: dict, avg_ms: float, sustained: bool) -> dict:
         peaks = self.peaks
@@ -835,7 +873,7 @@ class Runner:
                 "dtype": main["dtype"], "data": "synthetic", "config": cfg, "roofline": main["roofline"], "cpu_baseline": cpu,
                 "e2e": main.get("e2e"), "gpu_launches": args.steps, "clocks": main["clocks"],
             }
-            for k in ("local_gemm_ms", "frac_of_local_gemm_rate", "parity_max_rel_err", "parity", "comparators"):
+            for k in ("local_gemm_ms", "frac_of_local_gemm_rate", "parity_max_rel_err", "parity", "comparators", "in_kernel"):
                 if k in main:
                     line[k] = main[k]
             if extras:

@@ -29,7 +29,7 @@ namespace {
 
 using namespace gnk::gemm;
 
-std::atomic<long long*> g_trace{nullptr};  // test hook (gnk_debug_trace): device buffer of 2*2*256*3 int64
+std::atomic<long long*> g_trace{nullptr};  // test hook (gnk_debug_trace): device buffer of 2*2*256*3 + 4 int64
 std::atomic<int> g_max_clusters{0};  // test hook (gnk_debug_max_clusters): cap on the persistent grid, 0 = none
 
 template <MmaKind KIND>
@@ -258,7 +258,7 @@ extern "C" int gnk_debug_force_tile(int sel) {
   return GNK_OK;
 }
 
-// Debug: device buffer (2 CTAs x 2 roles x 256 stages x 3 int64 clock stamps) or NULL to stop tracing.
+// Debug: device buffer (2 CTAs x 2 roles x 256 stages x 3 int64 clock stamps + 4 int64 kernel span) or NULL to stop tracing.
 extern "C" int gnk_debug_trace(void* device_buffer) {
   g_trace = static_cast<long long*>(device_buffer);
   return GNK_OK;

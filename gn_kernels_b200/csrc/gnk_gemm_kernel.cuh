@@ -10,6 +10,7 @@ namespace gemm {
 enum Epi { EPI_BF16 = 0, EPI_ROWSCALED = 1, EPI_I32 = 2, EPI_RS = 3, EPI_GATED = 4 };
 constexpr int kMaxWorld = 8;  // ranks of one NVLink domain the reduce-scatter variant addresses
 constexpr int kTraceEvents = 256;  // stages recorded per (CTA, role) when tracing
+constexpr int kTraceSpanAt = 2 * 2 * kTraceEvents * 3;  // then 4 words: clock64 / globaltimer at entry and exit of CTA 0
 
 template <MmaKind K> struct KindInfo;
 template <> struct KindInfo<MmaKind::F16> { static constexpr bool kBlockScaled = false; static constexpr int kSfPerStage = 0; };
@@ -30,7 +31,7 @@ struct GemmArgs {
   const float* bias;
   float alpha;
   int vec_ok;  // C rows 16-byte aligned: vector stores allowed
-  long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1 (null = off)
+  long long* trace;  // debug: per-stage clock64 stamps of CTAs 0 and 1, then the kernel span of CTA 0 (null = off)
   int a_rows;        // rows of A one stage load brings in (the tensor map's box; 128 unless M < 128)
   int stages;        // pipeline depth (the launcher's choice: fewer A rows per stage leave room for more stages)
   int f16;           // kind::f16 only: bit 0 = operands are fp16 (else bf16), bit 1 = fp16 accumulator, bit 2 = fp16 output
@@ -533,6 +534,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
   const int num_tiles = g.tiles_m * g.tiles_n;
+  // tracing: SM cycle counter and wall clock at entry and exit of CTA 0 (their ratio is the SM clock
+  // the kernel really ran at)
+  long long* const kspan = g.trace && blockIdx.x == 0 && threadIdx.x == 0 ? g.trace + kTraceSpanAt : nullptr;
+  if (kspan) { kspan[0] = clock64(); kspan[1] = static_cast<long long>(globaltimer_ns()); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -983,6 +988,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, C::kTmemCols);
   }
+  if (kspan) { kspan[2] = clock64(); kspan[3] = static_cast<long long>(globaltimer_ns()); }
   if constexpr (EPI == EPI_RS) {
     // Exit barrier across ranks: a rank may start its next call (and overwrite staging slots on
     // its peers) only after every peer has finished reducing this one.  The last CTA of this rank
