@@ -52,9 +52,9 @@ _SIGNATURES = {
     "gnk_gemm_rs_flag_words": (c_int64, [c_int64, c_int64, c_int]),
     "gnk_gemm_rs_plan": (c_int64, [c_int64, c_int64, c_int, c_int, c_int64, POINTER(c_int32)]),
     "gnk_gemm_rs_bf16": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), POINTER(c_void_p), _P, c_int64, c_int64, c_int64,
-                                 c_int64, c_int, c_int, c_uint32, _P]),
+                                 c_int64, c_int, c_int, c_uint32, c_int, _P]),
     "gnk_gemm_rs_bf16_pull": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), _P, POINTER(c_void_p), _P, c_int64, c_int64,
-                                      c_int64, c_int64, c_int, c_int, c_uint32, _P]),
+                                      c_int64, c_int64, c_int, c_int, c_uint32, c_int, _P]),
     "gnk_debug_attn_trace": (c_int, [_P]),
     "gnk_debug_force_tile": (c_int, [c_int]),
     "gnk_debug_staged": (c_int, [c_int]),

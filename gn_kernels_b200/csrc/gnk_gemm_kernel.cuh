@@ -50,9 +50,12 @@ struct GemmArgs {
   } gated;
   // Reduce-scatter variant (EPI_RS): K-sharded partial tiles are pushed to the rank that owns
   // their rows and summed there.  staging[r] / flags[r] are rank r's buffers as mapped on
-  // THIS GPU.  Flag words: one per owned 128 x BN unit, then a CTA ticket, then the exit counter.
+  // THIS GPU.  Flag words: per owned 128 x BN unit one arrival and one progress word, then a CTA
+  // ticket, the exit counter (peers' "I have finished reducing" signals) and the count of calls
+  // whose exit wait was deferred.
   struct {
     int world, rank;
+    int lagged_exit;       // 1: this call signals its exit but leaves the wait to the next call's first store
     int rows_per_owner;    // M / world
     int tiles_per_owner;   // cluster tiles along M per owner
     unsigned int timeout_ms;
@@ -213,6 +216,21 @@ __device__ __forceinline__ bool wait_flag_eq(const unsigned int* p, unsigned int
   const uint64_t t0 = globaltimer_ns();
   const uint64_t budget = static_cast<uint64_t>(timeout_ms) * 1000000ull;
   while (ld_acquire_sys(p) != want) {
+    __nanosleep(64);
+    if (globaltimer_ns() - t0 > budget) {
+      report_timeout(detail);
+      return false;
+    }
+  }
+  return true;
+}
+// The same for a counter that only grows: done when it has reached `want`.
+__device__ __forceinline__ bool wait_flag_ge(const unsigned int* p, unsigned int want, unsigned int timeout_ms,
+                                             uint32_t detail) {
+  if (ld_acquire_sys(p) >= want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t budget = static_cast<uint64_t>(timeout_ms) * 1000000ull;
+  while (ld_acquire_sys(p) < want) {
     __nanosleep(64);
     if (globaltimer_ns() - t0 > budget) {
       report_timeout(detail);
@@ -748,6 +766,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     const uint32_t tempty0 = CG == 2 ? map_to_cta(bar_tempty(0), 0) : bar_tempty(0);
     const uint32_t partial = CG == 2 ? map_to_cta(bar_partial, 0) : bar_partial;
     bool ok = true;
+    [[maybe_unused]] bool first_tile = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
       int tm, tn;
       map_tile<EPI>(t, g, tm, tn);
@@ -755,6 +774,21 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       if (!mbar_wait(bar_tfull(acc), parity, (3u << 24) | (5u << 16) | acc)) { ok = false; break; }
       if (rs_tr) tr_wait += globaltimer_ns() - trw0;
       if constexpr (EPI == EPI_RS) {
+        // Entry half of a deferred exit barrier: earlier calls on these buffers may have left without
+        // waiting for their peers.  Nothing of this call may become visible to a peer (tile data, flag
+        // signals) before every peer has finished reducing the previous one; the first tile's main loop
+        // has run in the meantime.
+        if (first_tile) {
+          first_tile = false;
+          if (lane == 0 && g.rs.world > 1) {
+            const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;
+            const unsigned int* my_flags = g.rs.flags[g.rs.rank];
+            const unsigned int deferred = *reinterpret_cast<const volatile unsigned int*>(my_flags + 2 * units + 2);
+            if (deferred != 0u && !status_is_set())
+              wait_flag_ge(my_flags + 2 * units + 1, deferred * (g.rs.world - 1), g.rs.timeout_ms, (3u << 24) | (8u << 16));
+          }
+          __syncwarp();
+        }
         // Signal the warp's previous piece: by now its bulk stores have long completed, so this
         // wait returns at once; it also frees the staging area for this tile.
         if (lane == 0 && pending_flag) {
@@ -990,25 +1024,34 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   }
   if (kspan) { kspan[2] = clock64(); kspan[3] = static_cast<long long>(globaltimer_ns()); }
   if constexpr (EPI == EPI_RS) {
-    // Exit barrier across ranks: a rank may start its next call (and overwrite staging slots on
-    // its peers) only after every peer has finished reducing this one.  The last CTA of this rank
-    // tells every peer, then waits (bounded) for the world - 1 peers to tell it.
+    // Exit barrier across ranks: a rank may overwrite what its peers read (its partial, or its slots
+    // in their staging buffers) only after every peer has finished reducing this call.  The last CTA
+    // of this rank tells every peer.  It then either waits (bounded) for the world - 1 peers to tell
+    // it, and leaves the words zero; or, with `lagged_exit`, returns at once and counts the call, and
+    // the NEXT call on these buffers does the wait before its first store (see the epilogue), by
+    // which time the slowest peer has normally long finished.  The exit word only grows while waits
+    // are deferred: call number c is over everywhere when it holds c * (world - 1).
     if (threadIdx.x == 0) {
       const int units = (g.rs.rows_per_owner / 128) * g.tiles_n;
       unsigned int* my_flags = g.rs.flags[g.rs.rank];
       __threadfence();
-      // flag words: [units] arrivals, [units] finished chunks, CTA ticket, exit barrier
+      // flag words: [units] arrivals, [units] finished chunks, CTA ticket, exit counter, deferred calls
       const unsigned int ticket = atomicAdd(my_flags + 2 * units, 1u);
       if (ticket == gridDim.x - 1) {
         my_flags[2 * units] = 0u;
+        const unsigned int calls = my_flags[2 * units + 2] + 1u;
         __threadfence_system();
         for (int p = 0; p < g.rs.world; ++p)
           if (p != g.rs.rank) red_release_sys_add(g.rs.flags[p] + 2 * units + 1, 1u);
-        // a call that has already given up somewhere does not wait a second time: the flag words are
-        // then left as they are and the caller re-zeroes them (see gnk_gemm_rs_bf16 in gnk.h)
-        if (!status_is_set() &&
-            wait_flag_eq(my_flags + 2 * units + 1, g.rs.world - 1, g.rs.timeout_ms, (4u << 24) | (7u << 16)))
+        if (g.rs.lagged_exit) {
+          my_flags[2 * units + 2] = calls;
+        } else if (!status_is_set() &&
+                   wait_flag_ge(my_flags + 2 * units + 1, calls * (g.rs.world - 1), g.rs.timeout_ms, (4u << 24) | (7u << 16))) {
+          // a call that has already given up somewhere does not wait a second time: the flag words are
+          // then left as they are and the caller re-zeroes them (see gnk_gemm_rs_bf16 in gnk.h)
           my_flags[2 * units + 1] = 0u;
+          my_flags[2 * units + 2] = 0u;
+        }
       }
     }
   }

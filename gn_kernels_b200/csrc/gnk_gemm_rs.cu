@@ -136,7 +136,7 @@ extern "C" int gnk_debug_rs_trace(void* device_buffer) {
 extern "C" int64_t gnk_gemm_rs_flag_words(int64_t M, int64_t N, int world) {
   RsPlan p;
   if (make_plan(M, N, world, &p) != GNK_OK) return -1;
-  return 2 * p.units + 2;  // arrivals and finished-chunk counts per unit, CTA ticket, exit barrier
+  return 2 * p.units + 3;  // arrivals and finished-chunk counts per unit, CTA ticket, exit counter, deferred calls
 }
 
 // Host-side restatement of the device tile order, for tests: sequence index i -> the 128 x BN
@@ -164,7 +164,7 @@ extern "C" int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, i
 namespace {
 int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging, const void* multicast,
                  int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N, int64_t K_local, int rank,
-                 int world, uint32_t timeout_ms, gnk_stream_t stream) {
+                 int world, uint32_t timeout_ms, int lagged_exit, gnk_stream_t stream) {
   if (!x || !w || !output || M <= 0 || N <= 0 || K_local <= 0) return GNK_ERR_BAD_ARG;
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return GNK_ERR_BAD_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(output)) return GNK_ERR_BAD_ALIGN;
@@ -190,6 +190,7 @@ int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c
   g.rs.rows_per_owner = p.rows_per_owner;
   g.rs.tiles_per_owner = p.tiles_per_owner;
   g.rs.timeout_ms = timeout_ms ? timeout_ms : 20000u;
+  g.rs.lagged_exit = lagged_exit ? 1 : 0;
   for (int r = 0; r < world; ++r) {
     if (!staging[r] || !flags[r] || !aligned16(staging[r])) return GNK_ERR_BAD_ARG;
     g.rs.staging[r] = static_cast<__nv_bfloat16*>(staging[r]);
@@ -205,16 +206,17 @@ int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c
 
 extern "C" int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
                                 int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
-                                int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream) {
+                                int64_t K_local, int rank, int world, uint32_t timeout_ms, int lagged_exit,
+                                gnk_stream_t stream) {
   return gemm_rs_impl(x, ldx, w, ldw, staging, nullptr, flags, output, ldo, M, N, K_local, rank, world, timeout_ms,
-                      stream);
+                      lagged_exit, stream);
 }
 
 extern "C" int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* partial,
                                      const void* partial_multicast, int32_t* const* flags, void* output, int64_t ldo,
                                      int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
-                                     gnk_stream_t stream) {
+                                     int lagged_exit, gnk_stream_t stream) {
   if (world > 1 && (!partial_multicast || !aligned16(partial_multicast))) return GNK_ERR_BAD_ARG;
   return gemm_rs_impl(x, ldx, w, ldw, partial, partial_multicast, flags, output, ldo, M, N, K_local, rank, world,
-                      timeout_ms, stream);
+                      timeout_ms, lagged_exit, stream);
 }

@@ -62,6 +62,7 @@ def gemm_rs(
     BN: int | None = None,
     timeout_ms: int = 0,
     multicast: bool | None = None,
+    lagged_exit: bool = False,
 ) -> torch.Tensor:
     """output[M/W, N] = sum over ranks of bf16(x_r @ w_r^T)[this rank's rows], fp32 summation.
 
@@ -72,7 +73,13 @@ def gemm_rs(
     buffer over NVLink and the owner reduces from its own memory.  `multicast` = None picks the
     first when the handle offers an address, True requires it, False forces the second.
     Device-side waits are bounded by `timeout_ms` (0 = 20 s); a wait that runs out is
-    reported by `gn_kernels_b200._lib.raise_on_device_error()`.  BN is accepted for upstream
+    reported by `gn_kernels_b200._lib.raise_on_device_error()`.
+    `lagged_exit=True` is for calls issued back to back on the same buffers (one per layer, say): the
+    call tells its peers that it has finished reducing and returns without waiting for them; the next
+    call on the same `flags` does that wait just before its first store, under its first tiles' math.
+    `output` is complete either way; `partial` and `flags` then belong to the sequence until a call
+    with `lagged_exit=False` ends it (or a host barrier across the ranks, then `flags.zero_()`).
+    BN is accepted for upstream
     compatibility; the tile shape is chosen from the problem shape."""
     assert dist.is_initialized()
     rank = dist.get_rank()
@@ -102,7 +109,7 @@ def gemm_rs(
                 lib().gnk_gemm_rs_bf16_pull(
                     ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(w.data_ptr()), w.stride(0), sp,
                     ctypes.c_void_p(mc), fp, ctypes.c_void_p(output.data_ptr()), output.stride(0), M, N, K, rank, world,
-                    timeout_ms, stream,
+                    timeout_ms, int(bool(lagged_exit)), stream,
                 ),
                 "gnk_gemm_rs_bf16_pull",
             )
@@ -111,7 +118,8 @@ def gemm_rs(
         check(
             lib().gnk_gemm_rs_bf16(
                 ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(w.data_ptr()), w.stride(0), sp, fp,
-                ctypes.c_void_p(output.data_ptr()), output.stride(0), M, N, K, rank, world, timeout_ms, stream,
+                ctypes.c_void_p(output.data_ptr()), output.stride(0), M, N, K, rank, world, timeout_ms,
+                int(bool(lagged_exit)), stream,
             ),
             "gnk_gemm_rs_bf16",
         )

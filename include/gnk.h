@@ -244,12 +244,20 @@ int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, int64_t i, i
  * Every rank stores each finished bf16 tile into the owner's staging slot for this rank and
  * bumps the owner's flag; the owner sums the `world` slots from its own memory in fp32 and
  * writes output [M/world, N] bf16; an exit barrier across ranks ends the call.
+ * lagged_exit = 0: the call signals its peers and waits for theirs before it returns, so on return
+ *   every buffer may be reused for anything, and the flag words are zero again.
+ * lagged_exit = 1 (calls issued back to back on the same buffers): the call signals its peers and
+ *   returns; the NEXT gnk_gemm_rs_bf16* call on the same flags waits for those signals before its
+ *   first store, while its first tiles are already being computed.  `output` is complete on return
+ *   as before, but staging / partial must not be written by anything else, and the last two flag words
+ *   stay non-zero, until a later call with lagged_exit = 0 (or a host barrier across the ranks followed
+ *   by zeroing the flags) has ended the sequence.
  * Shapes: M % (128*world) == 0 and N % 128 == 0, K_local % 8 == 0, world <= 8.  When M/world % 256 == 0 and
  * N % 256 == 0 the 2-CTA 256 x 256 tile with bulk-store epilogue runs, otherwise a 128 x 128 tile with
  * plain peer stores.  world == 1 degenerates to gnk_mm_bf16 into `output`.
  * Failure: all device-side waits are bounded by timeout_ms (0 = 20 s).  When a peer never signals, the
  * first wait of a CTA that runs out records GNK_ERR_TIMEOUT (gnk_device_status; detail = role 4,
- * barrier 6 = unit flag, 7 = exit barrier) and every later wait of the call returns at once, so a
+ * barrier 6 = unit flag, 7 = exit barrier; role 3, barrier 8 = the deferred exit wait of the previous call) and every later wait of the call returns at once, so a
  * call costs at most about 2 x timeout_ms; the rows it could not reduce are left unwritten.  After
  * GNK_ERR_TIMEOUT the flag words are NOT zero: before the buffers are used again every rank must
  * finish or abandon its call, clear the status (gnk_device_status(..., clear = 1)), zero its flags
@@ -258,18 +266,19 @@ int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, int64_t i, i
  * Replaces: gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496 `gemm_rs`. */
 int gnk_gemm_rs_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging,
                      int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N,
-                     int64_t K_local, int rank, int world, uint32_t timeout_ms, gnk_stream_t stream);
+                     int64_t K_local, int rank, int world, uint32_t timeout_ms, int lagged_exit,
+                     gnk_stream_t stream);
 
 /* Same operation for buffers that also have an NVLink multicast address (NVSwitch systems):
  * partial[r] are the ranks' [M, N] bf16 buffers (only partial[rank] is written, by this rank),
  * partial_multicast the multicast address of the same allocation.  A finished tile stays in the
  * rank's own buffer; the owner reads every 16-byte piece once with multimem.ld_reduce (fp32 adds in
- * the switch), as upstream does (sm100_gemm_rs.py:27-60, 283-327).  flags as above.
+ * the switch), as upstream does (sm100_gemm_rs.py:27-60, 283-327).  flags and lagged_exit as above.
  * Replaces: gn_kernels/cutedsl/sm100/sm100_gemm_rs.py:458-496 `gemm_rs`. */
 int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* partial,
                           const void* partial_multicast, int32_t* const* flags, void* output, int64_t ldo,
                           int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
-                          gnk_stream_t stream);
+                          int lagged_exit, gnk_stream_t stream);
 
 /* ------------------------------------------------------------------ test hooks ---- */
 /* Process-wide switches for tests and profiling; none of them changes a result.

@@ -90,6 +90,27 @@ def main():
             dist.barrier()  # a faster peer's next call may signal this rank's flags as soon as it starts
         dist.barrier()
 
+        # A sequence with the exit wait deferred: four calls back to back with no host synchronisation in
+        # between, the ranks deliberately out of step (each spins a different time first), then one
+        # ordinary call that ends the sequence.  Every call's output must be right and the flags zero again.
+        seq = [torch.zeros_like(out) for _ in range(5)]
+        torch.cuda._sleep(200_000 * (1 + (rank * 3) % W))
+        for o in seq[:4]:
+            gemm_rs(x, w, partial, ph, o, flags, fh, lagged_exit=True)
+        gemm_rs(x, w, partial, ph, seq[4], flags, fh)
+        torch.cuda.synchronize()
+        _lib.raise_on_device_error()
+        assert int(flags.abs().sum()) == 0, "flags not restored to zero after the deferred-exit sequence"
+        for i, o in enumerate(seq):
+            outs = [torch.empty_like(o) for _ in range(W)]
+            dist.all_gather(outs, o)
+            if rank == 0:
+                errs = [max_rel_err(t.cpu(), r) for t, r in zip(outs, refs)]
+                ok = max(errs) <= 1e-2
+                print(f"gemm_rs W={W} M={M} N={N} K={Kl * W} deferred-exit sequence, call {i}: max rel err {max(errs):.2e} {'OK' if ok else 'FAIL'}", flush=True)
+                failures += 0 if ok else 1
+        dist.barrier()
+
     if args.trace:
         # per-role timeline of one full-size call (M = N = 8192): the kernel writes globaltimer stamps per CTA
         # into a caller-owned buffer (gnk_debug_rs_trace); rank 0 prints a summary in microseconds

@@ -90,5 +90,5 @@ def test_gemm_rs_pull_entry_refuses_a_missing_multicast_address():
     buf = (ctypes.c_char * 4096)()
     p = ctypes.c_void_p(ctypes.addressof(buf) // 16 * 16 + 16)
     arr = (ctypes.c_void_p * 2)(p, p)
-    rc = L.gnk_gemm_rs_bf16_pull(p, 64, p, 64, arr, ctypes.c_void_p(0), arr, p, 256, 512, 256, 64, 0, 2, 0, ctypes.c_void_p(0))
+    rc = L.gnk_gemm_rs_bf16_pull(p, 64, p, 64, arr, ctypes.c_void_p(0), arr, p, 256, 512, 256, 64, 0, 2, 0, 0, ctypes.c_void_p(0))
     assert rc == _lib.ERR_BAD_ARG

@@ -26,7 +26,7 @@ def _call_rank0_of_2(L, x, w, staging, flags, out, timeout_ms):
     sp = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in staging])
     fp = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in flags])
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    return L.gnk_gemm_rs_bf16(_p(x), K, _p(w), K, sp, fp, _p(out), N, M, N, K, 0, 2, timeout_ms, stream)
+    return L.gnk_gemm_rs_bf16(_p(x), K, _p(w), K, sp, fp, _p(out), N, M, N, K, 0, 2, timeout_ms, 0, stream)
 
 
 @pytest.mark.parametrize(
@@ -117,7 +117,7 @@ def test_two_ranks_one_after_the_other_on_one_gpu(M, N, K):
     def call(rank, staging, flags, out, timeout_ms):
         sp = (ctypes.c_void_p * W)(*[t.data_ptr() for t in staging])
         fp = (ctypes.c_void_p * W)(*[t.data_ptr() for t in flags])
-        return L.gnk_gemm_rs_bf16(_p(xs[rank]), K, _p(ws[rank]), K, sp, fp, _p(out), N, M, N, K, rank, W, timeout_ms, stream)
+        return L.gnk_gemm_rs_bf16(_p(xs[rank]), K, _p(ws[rank]), K, sp, fp, _p(out), N, M, N, K, rank, W, timeout_ms, 0, stream)
 
     for second in range(W):  # the rank whose output is checked runs second
         first = 1 - second
