@@ -203,7 +203,7 @@ def _nbytes(ts) -> int:
 # ------------------------------------------------------------------------------------------
 # GPU arm: workloads
 # ------------------------------------------------------------------------------------------
-def build_gpu_workload(name: str, dev: torch.device, timeout_ms: int = 2000, rs_lagged_exit: bool = True) -> dict:
+def build_gpu_workload(name: str, dev: torch.device, timeout_ms: int = 2000, rs_lagged_exit: bool = False) -> dict:
     """Operands resident on `dev`.  Returns step() (C ABI, preallocated outputs), api (the public
     Python call on device tensors), comparators (library calls of the same problem) and the accounting."""
     import gn_kernels_b200 as gk
@@ -319,7 +319,7 @@ def build_gpu_workload(name: str, dev: torch.device, timeout_ms: int = 2000, rs_
             path = "pull: multimem.ld_reduce on the NVLink multicast address" if getattr(ph, "multicast_ptr", 0) else "push: bulk stores into the owner's slots"
 
             def step():
-                # back-to-back calls on the same buffers: each call leaves its exit wait to the next one
+                # every call ends with the exit barrier across the ranks unless --rs-lagged-exit defers it
                 gemm_rs(x, wt, partial, ph, out, flags, fh, timeout_ms=timeout_ms, lagged_exit=rs_lagged_exit)
                 return 0
 
@@ -639,7 +639,7 @@ class Runner:
         from gn_kernels_b200 import _lib
 
         args = self.args
-        w = build_gpu_workload(name, self.dev, args.timeout_ms, not args.rs_sync_exit)
+        w = build_gpu_workload(name, self.dev, args.timeout_ms, args.rs_lagged_exit)
         step = w["step"]
         flush = w["resident_bytes"] < 1.5 * L2_BYTES  # operands could stay in L2 between steps: flush it
         warm = max(warmup, 3)
@@ -896,7 +896,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="gnk", choices=["gnk", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=512, help="rows of the CPU sample (bounded host time)")
-    ap.add_argument("--rs-sync-exit", action="store_true", help="reduce-scatter: wait for the peers at the end of every call instead of before the next call's first store")
+    ap.add_argument("--rs-lagged-exit", action="store_true", help="reduce-scatter: wait for the peers before the next call's first store instead of at the end of every call")
     ap.add_argument("--timeout-ms", type=int, default=2000, help="bound of the device-side waits of the reduce-scatter")
     ap.add_argument("--no-extra", action="store_true", help="main line only")
     ap.add_argument("--kernel-only", action="store_true", help="timed kernel launches only (for profiler captures): no comparators, parity, e2e, CPU arm, extras")
