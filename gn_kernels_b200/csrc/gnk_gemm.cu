@@ -40,10 +40,10 @@ struct ElemInfo {
   static constexpr int kSfBlock = KIND == MmaKind::MXF8F6F4 ? 32 : 16;
 };
 
-template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1>
+template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1, int KD = 1>
 int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_t* SFA, const uint8_t* SFB,
            GemmArgs g, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
-  using C = Cfg<KIND, BN, CG, EPI, STG>;
+  using C = Cfg<KIND, BN, CG, EPI, STG, KD>;
   using EI = ElemInfo<KIND>;
   const int64_t k_bytes = K * EI::kNum / EI::kDen;
   const int64_t lda_b = lda * EI::kNum;  // ld counts stored elements (bytes for packed fp4)
@@ -54,29 +54,44 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   const uint32_t box_inner = KIND == MmaKind::F16 ? 64 : 128;
   g.a_rows = M < 128 ? static_cast<int>((M + 7) / 8 * 8) : 128;
   g.stages = C::stages_for(g.a_rows);
-  int rc = make_tmap_2d(&tm_a, dt, A, M, k_elems_tm, lda_b, g.a_rows, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != GNK_OK) return rc;
-  rc = make_tmap_2d(&tm_b, dt, Bt, N, k_elems_tm, ldb_b, BN / CG, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != GNK_OK) return rc;
+  int rc;
+  if constexpr (KD > 1) {
+    // the operand seen as (128 bytes of K, rows, K slices): one box brings KD slices of the tile's rows
+    if (k_bytes % 128 != 0) return GNK_ERR_BAD_SHAPE;
+    const uint64_t slices = static_cast<uint64_t>(k_bytes / 128);
+    const uint64_t dims_a[4] = {box_inner, static_cast<uint64_t>(M), slices, 1};
+    const uint64_t dims_b[4] = {box_inner, static_cast<uint64_t>(N), slices, 1};
+    const uint64_t str_a[3] = {static_cast<uint64_t>(lda_b), 128, static_cast<uint64_t>(lda_b)};
+    const uint64_t str_b[3] = {static_cast<uint64_t>(ldb_b), 128, static_cast<uint64_t>(ldb_b)};
+    const uint32_t box_a[4] = {box_inner, static_cast<uint32_t>(g.a_rows), KD, 1};
+    const uint32_t box_b[4] = {box_inner, BN / CG, KD, 1};
+    if ((rc = make_tmap_4d(&tm_a, dt, A, dims_a, str_a, box_a, CU_TENSOR_MAP_SWIZZLE_128B)) != GNK_OK) return rc;
+    if ((rc = make_tmap_4d(&tm_b, dt, Bt, dims_b, str_b, box_b, CU_TENSOR_MAP_SWIZZLE_128B)) != GNK_OK) return rc;
+  } else {
+    rc = make_tmap_2d(&tm_a, dt, A, M, k_elems_tm, lda_b, g.a_rows, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != GNK_OK) return rc;
+    rc = make_tmap_2d(&tm_b, dt, Bt, N, k_elems_tm, ldb_b, BN / CG, box_inner, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != GNK_OK) return rc;
+  }
   if constexpr (C::KI::kBlockScaled) {
     // swizzled scale buffer seen as [row groups of 128][K/(4 scales) atoms of 512 bytes], in 8-byte words
     const int64_t ks = (K + EI::kSfBlock - 1) / EI::kSfBlock;
     const int64_t atoms = (ks + 3) / 4;
     rc = make_tmap_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_UINT64, SFA, (M + 127) / 128, atoms * 64, atoms * 512, 1,
-                      C::kSfAtomBytes / 8, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      C::kSfaBytes / C::kSfLoadsPerStage / 8, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != GNK_OK) return rc;
     rc = make_tmap_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT64, SFB, (N + 127) / 128, atoms * 64, atoms * 512,
-                      C::kSfbGroups, C::kSfAtomBytes / 8, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      C::kSfbGroups, C::kSfaBytes / C::kSfLoadsPerStage / 8, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != GNK_OK) return rc;
   } else {
     tm_sfa = tm_a;
     tm_sfb = tm_b;
   }
-  g.k_iters = static_cast<int>((k_bytes + 127) / 128);
+  g.k_iters = static_cast<int>((k_bytes + 128 * KD - 1) / (128 * KD));
   g.tiles_m = static_cast<int>((M + 128 * CG - 1) / (128 * CG));
   g.tiles_n = static_cast<int>((N + BN - 1) / BN);
   const int tiles = g.tiles_m * g.tiles_n;
-  auto kern = gemm_kernel<KIND, BN, CG, EPI, STG>;
+  auto kern = gemm_kernel<KIND, BN, CG, EPI, STG, KD>;
   // Persistent grid = the number of clusters that can be resident at once.  For 2-CTA
   // clusters this can be below SMs / 2 (both CTAs must land on one SM pair), and a cluster
   // that does not fit the first wave would run its whole share of tiles after everyone else.
@@ -194,6 +209,7 @@ int launch_gated(const void* X, int64_t ldx, const uint8_t* SFX, const void* W1,
 enum TileSel { T_2x256, T_1x256, T_1x128, T_1x64 };
 std::atomic<int> g_force_tile{-1};  // test hook (gnk_debug_force_tile)
 std::atomic<int> g_staged{-1};      // test hook (gnk_debug_staged)
+std::atomic<int> g_deep_stage{1};   // test hook (gnk_debug_deep_stage): 0 keeps one K slice per stage everywhere
 
 TileSel pick_tile(int64_t M, int64_t N, bool block_scaled) {
   const int forced = g_force_tile.load();
@@ -218,6 +234,19 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
     case T_1x256: return launch<KIND, 256, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x128: return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x64:
+      // One tile per CTA, a long K: the weight stream of a decode step.  The block-scaled kinds then move
+      // four (or two) 128-byte K slices per pipeline stage (rank-3 boxes), which divides the per-byte cost
+      // of the producer and issuer loops that bound this shape.
+      if constexpr (kBS && EPI == EPI_BF16) {
+        const int64_t k_bytes = KIND == MmaKind::MXF4NVF4 ? K / 2 : K;
+        const int64_t tiles = ((M + 127) / 128) * ((N + 63) / 64);
+        if (g_deep_stage.load() != 0 && k_bytes % 128 == 0 && k_bytes >= 2048 && tiles <= num_sms()) {
+          // the rows of A share the stage with the weight slices: few rows leave room for four slices
+          // per stage, more rows for two (the bytes of B in flight are what hides the DRAM latency)
+          if (M <= 32) return launch<KIND, 64, 1, EPI, 1, 4>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+          return launch<KIND, 64, 1, EPI, 1, 2>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
+        }
+      }
       return launch<KIND, 64, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
   }
   return GNK_ERR_UNSUPPORTED;
@@ -261,6 +290,13 @@ extern "C" int gnk_debug_force_tile(int sel) {
 // Debug: device buffer (2 CTAs x 2 roles x 256 stages x 3 int64 clock stamps + 4 int64 kernel span) or NULL to stop tracing.
 extern "C" int gnk_debug_trace(void* device_buffer) {
   g_trace = static_cast<long long*>(device_buffer);
+  return GNK_OK;
+}
+
+// Debug: 0 = the 64-wide tile always moves one 128-byte K slice per stage, 1 (default) = four slices per
+// stage where the shape qualifies.
+extern "C" int gnk_debug_deep_stage(int on) {
+  g_deep_stage = on;
   return GNK_OK;
 }
 

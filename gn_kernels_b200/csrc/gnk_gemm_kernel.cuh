@@ -22,7 +22,7 @@ template <> struct KindInfo<MmaKind::MXF4NVF4> { static constexpr bool kBlockSca
 
 struct GemmArgs {
   int M, N;
-  int k_iters;           // K stages of 128 bytes
+  int k_iters;           // pipeline stages along K (128 bytes of K per row each, times the kernel's KD)
   int tiles_m, tiles_n;  // cluster tiles: (128 * CG) x BN
   void* C;
   int64_t ldc;
@@ -99,9 +99,14 @@ __device__ __forceinline__ const CUtensorMap* output_map<EPI_RS>(const EpiMaps<E
   return &m.slot[0];  // never used: the reduce-scatter variant stores through slot[owner]
 }
 
-template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16, int STG = 1>
+// KD = 128-byte K slices per pipeline stage.  A problem that is one stream of a weight matrix past a
+// few rows of activations (one tile per CTA) is bound by the per-stage cost of the producer and issuer
+// loops (barrier round trips, TMA issue), not by bytes or math: KD = 4 moves 512 bytes of K per row
+// with the same number of operations (one rank-3 box per operand).
+template <MmaKind KIND, int BN, int CG, int EPI = EPI_BF16, int STG = 1, int KD = 1>
 struct Cfg {
   using KI = KindInfo<KIND>;
+  static_assert(KD == 1 || (CG == 1 && BN <= 128), "deep stages are for the small single-CTA tiles");
   // bf16 outputs of the 256-wide pair tile leave through per-warp shared-memory staging and bulk
   // tensor stores.  Plain GEMMs (STG != 0): two 4 KB buffers per warp, one 64-column block each,
   // so only 32 KB of pipeline space is given up.  The reduce-scatter variant stages the whole
@@ -109,22 +114,27 @@ struct Cfg {
   static constexpr bool kStaged = EPI == EPI_RS && BN == 256 && CG == 2;
   static constexpr bool kBulkC = STG != 0 && BN == 256 && CG == 2 && EPI != EPI_I32 && EPI != EPI_RS && EPI != EPI_GATED;
   static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : kBulkC ? 4 * 2 * 4096 : 0;
-  static constexpr int kABytes = 128 * 128;
-  static constexpr int kBBytes = (BN / CG) * 128;
-  static constexpr int kSfAtomBytes = 128 * KI::kSfPerStage;           // one 128-row group, one stage
-  static constexpr int kSfaBytes = kSfAtomBytes;
+  static constexpr int kABytes = 128 * 128 * KD;
+  static constexpr int kBSliceBytes = (BN / CG) * 128;                 // one 128-byte K slice of the B tile
+  static constexpr int kBBytes = kBSliceBytes * KD;
+  static constexpr int kSfAtomBytes = 128 * KI::kSfPerStage;           // one 128-row group, one K slice
+  static constexpr int kSfaBytes = kSfAtomBytes * KD;
   static constexpr int kSfbGroups = BN >= 128 ? BN / 128 : 1;
-  static constexpr int kSfbBytes = kSfAtomBytes * kSfbGroups;
+  static constexpr int kSfbBytes = kSfAtomBytes * kSfbGroups * KD;
+  static constexpr int kSfLoadsPerStage = (kSfaBytes / 8 + 255) / 256;  // TMA boxes are at most 256 elements wide
+  static_assert(KD == 1 || kSfbGroups == 1, "deep stages load the scale atoms of one 128-row group of B");
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kSmemBudget = 227 * 1024 - 2048 - kEpiBytes;    // barriers + alignment slack
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2048 + kEpiBytes;
+  // deep stages are coarse (up to 100 KB): they get the whole budget rather than a multiple of the full-size stage
+  static constexpr int kSmemBytes = KD > 1 ? kSmemBudget + 2048 + kEpiBytes : kStages * kStageBytes + 2048 + kEpiBytes;
   static constexpr int kMaxStages = 24;  // barrier words stay well inside the 2 KB reserve
   // pipeline depth when a stage holds only a_rows rows of A
   static int stages_for(int a_rows) {
-    if (a_rows >= 128) return kStages;
-    const int n = (kStages * kStageBytes) / (kStageBytes - (128 - a_rows) * 128);
+    if (a_rows >= 128 && KD == 1) return kStages;
+    const int pool = KD > 1 ? kSmemBudget : kStages * kStageBytes;
+    const int n = pool / (kStageBytes - (128 - a_rows) * 128 * KD);
     return n > kMaxStages ? kMaxStages : n;
   }
   // TMEM columns
@@ -324,6 +334,22 @@ __device__ __forceinline__ void drain_cols(uint32_t taddr_row, int c0, int c1, c
   }
 }
 
+// the same for a result that two issuing threads accumulated in two places: columns [0, c1) of the
+// accumulator at taddr_row plus the same columns `other` columns further on (fp32 kinds)
+template <MmaKind KIND, int EPI>
+__device__ __forceinline__ void drain_cols_sum2(uint32_t taddr_row, uint32_t other, int c1, const GemmArgs& g, int row,
+                                                int ncol0, float sa, void* rowptr) {
+  for (int c = 0; c + 32 <= c1; c += 32) {
+    uint32_t r[32], q[32];
+    tmem_ld32(taddr_row + c, r);
+    tmem_ld32(taddr_row + other + c, q);
+    tc_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
+    store_cols<KIND, EPI, 32>(r, g, row, ncol0 + c, sa, rowptr);
+  }
+}
+
 // Reducer: one chunk of PB * 128 / (BN / 8) rows x BN columns of this rank's output.  Each of the 128
 // reducer threads owns PB 16-byte pieces; the loads of all slots of all its pieces are in flight
 // together (PB * world <= 16), the fp32 sums run in rank order, the result is rounded to bf16 once.
@@ -510,19 +536,26 @@ __device__ __forceinline__ void stage_cols16_sw128(const uint32_t (&raw)[16], in
   }
 }
 
-template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1>
+template <MmaKind KIND, int BN, int CG, int EPI, int STG = 1, int KD = 1>
 __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320 : 192, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                 const __grid_constant__ EpiMaps<EPI> epi_maps, const GemmArgs g) {
-  using C = Cfg<KIND, BN, CG, EPI, STG>;
+  using C = Cfg<KIND, BN, CG, EPI, STG, KD>;
   constexpr bool kBS = C::KI::kBlockScaled;
+  // Deep stages have TWO issuing threads.  One thread issues a tcgen05 instruction every ~35 cycles, and
+  // a weight stream past a few rows of activations needs K/32 MMAs plus the scale copies per CTA whatever
+  // the tile width: that issue time, not bytes or math, bounds the kernel.  Warp 5 takes the first half
+  // of a stage's K slices into accumulator 0, warp 3 (idle until its epilogue) the second half into
+  // accumulator 1 with scale columns of its own; the epilogue adds the two.  Such a CTA has one tile.
+  constexpr int kIssuers = KD > 1 ? 2 : 1;
   // A problem with fewer than 128 rows loads and holds only those rows of A per stage (rows beyond
   // them read stale shared memory and only feed accumulator rows that are never stored).  A skinny
   // GEMM is the DRAM stream of B, and its rate is set by the bytes in flight: the space saved on A
   // goes into more pipeline stages.
   const int S = g.stages;
-  const uint32_t a_bytes = static_cast<uint32_t>(g.a_rows) * 128u;
+  const uint32_t a_slice = static_cast<uint32_t>(g.a_rows) * 128u;  // one 128-byte K slice of the A tile
+  const uint32_t a_bytes = a_slice * KD;
   constexpr int kInner = KIND == MmaKind::F16 ? 64 : 128;  // tensor-map elements per 128-byte K stage
 
   extern __shared__ uint8_t smem_raw[];
@@ -560,10 +593,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(bar_full(s), CG);  // one expect_tx arrival per CTA of the pair
-      mbar_init(bar_empty(s), 1);  // one tcgen05.commit
+      mbar_init(bar_empty(s), kIssuers);  // one tcgen05.commit per issuing thread
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_tfull(s), 1);
+      mbar_init(bar_tfull(s), kIssuers);
       mbar_init(bar_tempty(s), 4 * CG);  // one arrival per epilogue warp of every CTA
     }
     mbar_init(bar_partial, 4 * CG);
@@ -598,6 +631,66 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     }
   }
 
+  constexpr uint32_t kIdesc = KIND == MmaKind::F16      ? idesc_dense(1, 1, 1, 128 * CG, BN)
+                              : KIND == MmaKind::I8     ? idesc_dense(2, 1, 1, 128 * CG, BN)
+                              : KIND == MmaKind::F8F6F4 ? idesc_dense(1, 0, 0, 128 * CG, BN)
+                              : KIND == MmaKind::MXF8F6F4 ? idesc_block_scaled(0, 1, 128 * CG, BN)
+                                                          : idesc_block_scaled(1, 0, 128 * CG, BN);
+  uint32_t idesc = kIdesc;
+  if constexpr (KIND == MmaKind::F16 && EPI == EPI_BF16) {
+    if (g.f16 & 1) idesc &= ~((7u << 7) | (7u << 10));  // operand formats: F16 = 0 (BF16 = 1)
+    if (g.f16 & 2) idesc &= ~(3u << 4);                 // accumulator format: F16 = 0 (F32 = 1)
+  }
+  // The tcgen05 instructions of K slices [d0, d1) of a stage: scale copies, then four MMAs per slice, then
+  // the commit that frees the stage.  Called by all 32 lanes: the descriptors are computed warp-uniformly
+  // and only the issue instructions sit in the elected lane's region.
+  auto issue_slices = [&](bool leader, uint32_t stage, int k, int d0, int d1, uint32_t d_tmem, uint32_t sf_tmem,
+                          uint32_t sfb_half) {
+    uint64_t a_desc[KD], b_desc[KD], sfa_desc[KD], sfb_desc[KD];
+#pragma unroll
+    for (int d = 0; d < KD; ++d) {
+      a_desc[d] = sdesc_k128(stage_a(stage) + d * a_slice);
+      b_desc[d] = sdesc_k128(stage_b(stage) + d * C::kBSliceBytes);
+      // scale atoms of a stage: [row group][K slice]
+      sfa_desc[d] = sdesc_sf(stage_sfa(stage) + d * C::kSfAtomBytes);
+      sfb_desc[d] = sdesc_sf(stage_sfb(stage) + d * C::kSfAtomBytes);
+    }
+    const uint32_t empty = bar_empty(stage);
+    if (leader) {
+#pragma unroll
+      for (int d = 0; d < KD; ++d) {
+        if (d < d0 || d >= d1) continue;
+        if constexpr (kBS) {
+          constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per K slice: 1 (mxfp8) or 4 (nvfp4)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a) {
+            tc_cp_sf<CG>(sf_tmem + 4 * a, sfa_desc[d] + (512 >> 4) * a);
+#pragma unroll
+            for (int j = 0; j < C::kSfbGroups; ++j)
+              tc_cp_sf<CG>(sf_tmem + C::kSfaCols + (a * C::kSfbGroups + j) * 4,
+                           sfb_desc[d] + ((j * C::kSfAtomBytes * KD + 512 * a) >> 4));
+          }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint32_t accum = (k | (d - d0) | kk) != 0;
+          if constexpr (!kBS) {
+            tc_mma<KIND, CG>(d_tmem, a_desc[d] + 2 * kk, b_desc[d] + 2 * kk, idesc, accum);
+          } else if constexpr (KIND == MmaKind::MXF8F6F4) {
+            // the four K steps of a slice read bytes 0..3 of the same scale columns (scale ids in the descriptor)
+            tc_mma_bs<KIND, CG>(d_tmem, a_desc[d] + 2 * kk, b_desc[d] + 2 * kk, idesc | (kk << 4) | (kk << 29), sf_tmem,
+                                sf_tmem + C::kSfaCols + sfb_half, accum);
+          } else {
+            // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
+            tc_mma_bs<KIND, CG>(d_tmem, a_desc[d] + 2 * kk, b_desc[d] + 2 * kk, idesc, sf_tmem + 4 * kk,
+                                sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4 + sfb_half, accum);
+          }
+        }
+      }
+      if constexpr (CG == 2) tc_commit_pair(empty, 3); else tc_commit<1>(empty);
+    }
+  };
+
   // Producer and MMA warps run their loops warp-uniformly (all 32 lanes wait on the barriers and
   // compute addresses and descriptors, which keeps those values in uniform registers); one
   // elected lane executes the TMA / tcgen05 issue instructions.
@@ -606,7 +699,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     const bool leader = elect_one();
     uint32_t stage = 0, parity = 1;
     bool ok = true;
-    const uint32_t stage_tx = C::kStageBytes - (128 - g.a_rows) * 128;
+    const uint32_t stage_tx = C::kStageBytes - (128 - g.a_rows) * 128 * KD;
     // both CTAs of a pair count their bytes on CTA 0's barrier
     const uint32_t full0 = CG == 2 ? map_to_cta(bar_full(0), 0) : bar_full(0);
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
@@ -651,6 +744,23 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
               tma_load_2d_pair(stage_sfa(stage), &tm_sfa, full, k * (C::kSfAtomBytes / 8), sfa_row);
               tma_load_2d_pair(stage_sfb(stage), &tm_sfb, full, k * (C::kSfAtomBytes / 8), sfb_row);
             }
+          } else if constexpr (KD > 1) {
+            // rank-3 boxes (128 bytes of K, rows, KD slices): the slices land one after the other, each in
+            // the layout of an ordinary stage; the scale atoms of consecutive slices are contiguous anyway
+            mbar_expect_tx(full, stage_tx);
+            tma_load_4d(sa, &tm_a, full, 0, a_row, k * KD, 0);
+            tma_load_4d(sb, &tm_b, full, 0, b_row, k * KD, 0);
+            if constexpr (kBS) {
+              // a box is at most 256 eight-byte words wide: all KD atoms of MXFP8 in one, one per slice for NVFP4
+              constexpr int kSfLoads = C::kSfLoadsPerStage;
+#pragma unroll
+              for (int q = 0; q < kSfLoads; ++q) {
+                tma_load_2d(stage_sfa(stage) + q * (C::kSfaBytes / kSfLoads), &tm_sfa, full,
+                            (k * kSfLoads + q) * (C::kSfaBytes / kSfLoads / 8), sfa_row);
+                tma_load_2d(stage_sfb(stage) + q * (C::kSfaBytes / kSfLoads), &tm_sfb, full,
+                            (k * kSfLoads + q) * (C::kSfaBytes / kSfLoads / 8), sfb_row);
+              }
+            }
           } else {
             mbar_expect_tx(full, stage_tx);
             tma_load_2d(sa, &tm_a, full, k * kInner, a_row);
@@ -676,16 +786,6 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       const bool leader = elect_one();
       uint32_t stage = 0, parity = 0, acc = 0, acc_parity = 1, iter = 0;
       bool ok = true;
-      constexpr uint32_t kIdesc = KIND == MmaKind::F16      ? idesc_dense(1, 1, 1, 128 * CG, BN)
-                                  : KIND == MmaKind::I8     ? idesc_dense(2, 1, 1, 128 * CG, BN)
-                                  : KIND == MmaKind::F8F6F4 ? idesc_dense(1, 0, 0, 128 * CG, BN)
-                                  : KIND == MmaKind::MXF8F6F4 ? idesc_block_scaled(0, 1, 128 * CG, BN)
-                                                              : idesc_block_scaled(1, 0, 128 * CG, BN);
-      uint32_t idesc = kIdesc;
-      if constexpr (KIND == MmaKind::F16 && EPI == EPI_BF16) {
-        if (g.f16 & 1) idesc &= ~((7u << 7) | (7u << 10));  // operand formats: F16 = 0 (BF16 = 1)
-        if (g.f16 & 2) idesc &= ~(3u << 4);                 // accumulator format: F16 = 0 (F32 = 1)
-      }
       const uint32_t sf_tmem = tmem_base + C::kSfBase;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++iter) {
         if (!mbar_wait(bar_tempty(acc), acc_parity, (2u << 24) | (2u << 16) | acc)) { ok = false; break; }
@@ -706,39 +806,8 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
           if (!mbar_wait(bar_full(stage), parity, (2u << 24) | (4u << 16) | stage)) { ok = false; break; }
           const long long tr1 = g.trace ? clock64() : 0;
           tc_fence_after();
-          const uint64_t a_desc = sdesc_k128(stage_a(stage));
-          const uint64_t b_desc = sdesc_k128(stage_b(stage));
-          const uint64_t sfa_desc = sdesc_sf(stage_sfa(stage));
-          const uint64_t sfb_desc = sdesc_sf(stage_sfb(stage));
-          const uint32_t empty = bar_empty(stage);
+          issue_slices(leader, stage, k, 0, KD / kIssuers, d_tmem, sf_tmem, sfb_half);
           if (leader) {
-            if constexpr (kBS) {
-              constexpr int kAtoms = C::kSfAtomBytes / 512;  // atoms per 128-row group per stage: 1 (mxfp8) or 4 (nvfp4)
-#pragma unroll
-              for (int a = 0; a < kAtoms; ++a) {
-                tc_cp_sf<CG>(sf_tmem + 4 * a, sfa_desc + (512 >> 4) * a);
-#pragma unroll
-                for (int j = 0; j < C::kSfbGroups; ++j)
-                  tc_cp_sf<CG>(sf_tmem + C::kSfaCols + (a * C::kSfbGroups + j) * 4,
-                               sfb_desc + ((j * C::kSfAtomBytes + 512 * a) >> 4));
-              }
-            }
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint32_t accum = (k | kk) != 0;
-              if constexpr (!kBS) {
-                tc_mma<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, accum);
-              } else if constexpr (KIND == MmaKind::MXF8F6F4) {
-                // the four K steps of a stage read bytes 0..3 of the same scale columns (scale ids in the descriptor)
-                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc | (kk << 4) | (kk << 29), sf_tmem,
-                                    sf_tmem + C::kSfaCols + sfb_half, accum);
-              } else {
-                // each K step (64 fp4) has its own scale columns (4 scales = one 32-bit column per row group)
-                tc_mma_bs<KIND, CG>(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, sf_tmem + 4 * kk,
-                                    sf_tmem + C::kSfaCols + kk * C::kSfbGroups * 4 + sfb_half, accum);
-              }
-            }
-            if constexpr (CG == 2) tc_commit_pair(empty, 3); else tc_commit<1>(empty);
             if (g.trace && blockIdx.x < 2 && trace_it < kTraceEvents) {
               long long* tp = g.trace + ((blockIdx.x * 2 + 1) * kTraceEvents + trace_it) * 3;
               tp[0] = tr0; tp[1] = tr1; tp[2] = clock64();
@@ -759,6 +828,27 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       if (rs_tr && leader) rs_tr[4] = globaltimer_ns();
     }
   } else if (warp < 4) {
+    if constexpr (kIssuers == 2) {
+      // second issuing thread (see kIssuers): the upper half of every stage's K slices, accumulator 1,
+      // scale columns 32 further on; then this warp joins the epilogue like the others
+      if (warp == 3 && cluster_id < num_tiles) {
+        const bool leader = elect_one();
+        uint32_t stage = 0, parity = 0;
+        int tm, tn;
+        map_tile<EPI>(cluster_id, g, tm, tn);
+        const uint32_t sfb_half = (kBS && BN == 64) ? 2u * (tn & 1) : 0u;
+        bool ok = true;
+        for (int k = 0; k < g.k_iters; ++k) {
+          if (!mbar_wait(bar_full(stage), parity, (2u << 24) | (9u << 16) | stage)) { ok = false; break; }
+          tc_fence_after();
+          issue_slices(leader, stage, k, KD / 2, KD, tmem_base + C::kAccStride, tmem_base + C::kSfBase + 32, sfb_half);
+          __syncwarp();
+          if (++stage == S) { stage = 0; parity ^= 1; }
+        }
+        if (ok && leader) tc_commit<1>(bar_tfull(0));
+        __syncwarp();
+      }
+    }
     unsigned long long tr_store = 0, tr_wait = 0;
     unsigned int* pending_flag = nullptr;  // lane 0: flag of the piece whose bulk stores are still in flight
     // ------------------------------ epilogue (warps 0-3) ------------------------------
@@ -888,6 +978,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         drain_cols<KIND, EPI>(taddr_row, p0, p1, g, row, ncol0, sa, rowptr);
       } else {
         if constexpr (kBulkStore) drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, 0, BN, g, ncol0, sa, stg, lane);
+        else if constexpr (kIssuers == 2) drain_cols_sum2<KIND, EPI>(taddr_row, C::kAccStride, BN, g, row, ncol0, sa, rowptr);
         else drain_cols<KIND, EPI>(taddr_row, 0, BN, g, row, ncol0, sa, rowptr);
       }
       tc_fence_before();

@@ -309,7 +309,7 @@ def test_full_size_8192(gk, kind):
     assert bool((out.float().abs().amax(dim=1) > 0).all())
 
 
-@pytest.mark.parametrize("M", [16, 64, 128])
+@pytest.mark.parametrize("M", [1, 16, 64, 128])
 def test_mxfp8_skinny_decode_shapes(gk, M):
     N = K = 8192
     A = randn_bf16((M, K), 31)
@@ -319,6 +319,43 @@ def test_mxfp8_skinny_decode_shapes(gk, M):
     out = gk.cutedsl.sm100.sm100_mm_mxfp8.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb))
     ref = omm.mm_mxfp8(u8(Aq), u8(Bq), u8(sfa), u8(sfb))
     assert_parity(out, ref)
+
+
+@pytest.mark.parametrize("kind", ["mxfp8", "nvfp4"])
+@pytest.mark.parametrize("M,N,K", [(16, 2048, 4096), (100, 1024, 4096 + 384), (128, 4096 + 64, 8192), (8, 512, 6144 + 128)])
+def test_skinny_four_k_slices_per_stage(gk, kind, M, N, K):
+    """One tile per CTA and a long K take the pipeline with four (few rows) or two 128-byte K slices per
+    stage (rank-3 boxes) and two issuing threads, each with an accumulator of its own; the sum of the
+    two differs from the one-slice pipeline's single accumulator by fp32 rounding only.  K that is not
+    a multiple of the stage depth ends in zero-filled slices."""
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    A = randn_bf16((M, K), 61)
+    Bt = randn_bf16((N, K), 62)
+    if kind == "mxfp8":
+        Aq, sfa = gk.quantize_mx(A, torch.float8_e4m3fn)
+        Bq, sfb = gk.quantize_mx(Bt, torch.float8_e4m3fn)
+        run = lambda: gk.cutedsl.sm100.sm100_mm_mxfp8.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb))  # noqa: E731
+        ref = omm.mm_mxfp8(u8(Aq), u8(Bq), u8(sfa), u8(sfb))
+    else:
+        Aq, sfa, tsa = gk.quantize_nvfp4(A)
+        Bq, sfb, tsb = gk.quantize_nvfp4(Bt)
+        alpha = float(tsa) * float(tsb)
+        run = lambda: gk.cutedsl.sm100.sm100_mm_nvfp4.mm(Aq, Bq, gk.permute_nv_sf(sfa), gk.permute_nv_sf(sfb), alpha)  # noqa: E731
+        ref = omm.mm_nvfp4(u8(Aq), u8(Bq), u8(sfa), u8(sfb), np.float32(float(tsa)) * np.float32(float(tsb)))
+    try:
+        assert L.gnk_debug_force_tile(3) == 0  # the 128 x 64 tile, as the automatic choice makes for these shapes
+        out = run()
+        assert L.gnk_debug_deep_stage(0) == 0
+        one_slice = run()
+    finally:
+        L.gnk_debug_deep_stage(1)
+        L.gnk_debug_force_tile(-1)
+    assert_parity(out, ref)
+    assert_parity(one_slice, ref)
+    # the same products summed in another order: a few outputs move by one bf16 step
+    assert float((out.float() - one_slice.float()).abs().max()) <= 2.0**-7 * float(ref.float().abs().max())
 
 
 def test_strided_and_unaligned_operands(gk):
