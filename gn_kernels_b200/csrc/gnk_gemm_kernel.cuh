@@ -112,14 +112,15 @@ struct Cfg {
   // so only 32 KB of pipeline space is given up.  The reduce-scatter variant stages the whole
   // 32 x 256 piece (16 KB per warp) because it waits for completion once per tile.
   static constexpr bool kStaged = EPI == EPI_RS && BN == 256 && CG == 2;
-  static constexpr bool kBulkC = STG != 0 && BN == 256 && CG == 2 && EPI != EPI_I32 && EPI != EPI_RS && EPI != EPI_GATED;
+  static constexpr bool kBulkC = STG != 0 && (BN == 256 || BN == 192) && CG == 2 && EPI != EPI_I32 && EPI != EPI_RS && EPI != EPI_GATED;
   static constexpr int kEpiBytes = kStaged ? 4 * 32 * BN * 2 : kBulkC ? 4 * 2 * 4096 : 0;
   static constexpr int kABytes = 128 * 128 * KD;
   static constexpr int kBSliceBytes = (BN / CG) * 128;                 // one 128-byte K slice of the B tile
   static constexpr int kBBytes = kBSliceBytes * KD;
   static constexpr int kSfAtomBytes = 128 * KI::kSfPerStage;           // one 128-row group, one K slice
   static constexpr int kSfaBytes = kSfAtomBytes * KD;
-  static constexpr int kSfbGroups = BN >= 128 ? BN / 128 : 1;
+  // a 192-wide tile starts at row 0 or 64 of a 128-row scale group and touches two groups either way
+  static constexpr int kSfbGroups = BN >= 128 ? (BN + 127) / 128 : 1;
   static constexpr int kSfbBytes = kSfAtomBytes * kSfbGroups * KD;
   static constexpr int kSfLoadsPerStage = (kSfaBytes / 8 + 255) / 256;  // TMA boxes are at most 256 elements wide
   static_assert(KD == 1 || kSfbGroups == 1, "deep stages load the scale atoms of one 128-row group of B");
@@ -794,9 +795,10 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
-        // a 64-wide tile uses half of a 128-row scale atom of B: rows 64..127 sit in TMEM columns 2 and 3
+        // a 64-wide tile uses half of a 128-row scale atom of B: rows 64..127 sit in TMEM columns 2 and 3;
+        // every second 192-wide tile starts at row 64 of its first scale group in the same way
         uint32_t sfb_half = 0;
-        if constexpr (kBS && BN == 64) {
+        if constexpr (kBS && (BN == 64 || BN == 192)) {
           int tm, tn;
           map_tile<EPI>(t, g, tm, tn);
           sfb_half = 2u * (tn & 1);
@@ -856,6 +858,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
     const uint32_t tempty0 = CG == 2 ? map_to_cta(bar_tempty(0), 0) : bar_tempty(0);
     const uint32_t partial = CG == 2 ? map_to_cta(bar_partial, 0) : bar_partial;
     bool ok = true;
+    [[maybe_unused]] uint32_t stage_turn = 0;  // bulk-store epilogue: which of the warp's two staging buffers comes next
     [[maybe_unused]] bool first_tile = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
       int tm, tn;
@@ -918,15 +921,17 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
       const uint32_t stg = epi_smem + warp * (C::kBulkC ? 2 * 4096 : 32 * BN * 2);
       if constexpr (C::kBulkC) staged = g.vec_ok && (ncol0 + BN <= g.N);
       if (C::kBulkC && staged) {
-        // Four 64-column blocks, each: wait until the buffer's previous store has read it, drain the
+        // 64-column blocks, each: wait until the buffer's previous store has read it, drain the
         // block into it (swizzled), hand it to a bulk tensor store (rows beyond M are clipped).  With
         // overlapping accumulators the block holding the shared columns goes first.
         const int row0 = (tm * CG + cta_rank) * 128 + warp * 32;
         const int first = (C::kOverlap && acc == 0) ? 3 : 0;
+        constexpr int kBlocks = BN / 64;
 #pragma unroll 1
-        for (int i = 0; i < 4; ++i) {
-          const int cb = (first + i) & 3;
-          const uint32_t buf = stg + (i & 1) * 4096;
+        for (int i = 0; i < kBlocks; ++i) {
+          const int cb = C::kOverlap ? (first + i) & 3 : i;
+          // the two buffers alternate across tiles too (a 192-wide tile has an odd number of blocks)
+          const uint32_t buf = stg + (stage_turn++ & 1) * 4096;
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
           if (C::kOverlap && i == 0) {
@@ -951,7 +956,7 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
           } else {
             drain_to_smem_sw128<KIND, EPI, BN>(taddr_row, cb * 64, cb * 64 + 64, g, ncol0, sa, buf - cb * 4096, lane);
           }
-          if (i == 3) {
+          if (i == kBlocks - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * acc);

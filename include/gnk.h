@@ -282,7 +282,8 @@ int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw
 
 /* ------------------------------------------------------------------ test hooks ---- */
 /* Process-wide switches for tests and profiling; none of them changes a result.
- * Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, -1: automatic),
+ * Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, 4: 2-CTA 256x192 for
+ * the block-scaled kinds (256x256 for the others), -1: automatic),
  * cap the persistent grid (0 = no cap), record per-stage clock stamps of CTAs 0 and 1 into a
  * caller-owned device buffer of 2*2*256*3 + 4 int64 (NULL = off); the last four words are clock64 and
  * globaltimer (ns) at entry and at exit of CTA 0, whose ratio is the SM clock the launch ran at. */
