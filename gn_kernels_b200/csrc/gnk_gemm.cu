@@ -243,13 +243,14 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
     case T_1x256: return launch<KIND, 256, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x128: return launch<KIND, 128, 1, EPI>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
     case T_1x64:
-      // One tile per CTA, a long K: the weight stream of a decode step.  The block-scaled kinds then move
+      // One tile per CTA, a long K: the weight stream of a decode step.  The pipeline then moves
       // four (or two) 128-byte K slices per pipeline stage (rank-3 boxes), which divides the per-byte cost
       // of the producer and issuer loops that bound this shape.
-      if constexpr (kBS && EPI == EPI_BF16) {
-        const int64_t k_bytes = KIND == MmaKind::MXF4NVF4 ? K / 2 : K;
+      if constexpr (EPI != EPI_GATED && EPI != EPI_RS) {
+        const int64_t k_bytes = K * ElemInfo<KIND>::kNum / ElemInfo<KIND>::kDen;
         const int64_t tiles = ((M + 127) / 128) * ((N + 63) / 64);
-        if (g_deep_stage.load() != 0 && k_bytes % 128 == 0 && k_bytes >= 2048 && tiles <= num_sms()) {
+        // (not with an fp16 accumulator: the two issuing threads' partial sums are added as fp32 words)
+        if (g_deep_stage.load() != 0 && !(g.f16 & 2) && k_bytes % 128 == 0 && k_bytes >= 2048 && tiles <= num_sms()) {
           // the rows of A share the stage with the weight slices: few rows leave room for four slices
           // per stage, more rows for two (the bytes of B in flight are what hides the DRAM latency)
           if (M <= 32) return launch<KIND, 64, 1, EPI, 1, 4>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);

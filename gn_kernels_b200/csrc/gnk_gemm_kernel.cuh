@@ -131,11 +131,16 @@ struct Cfg {
   // deep stages are coarse (up to 100 KB): they get the whole budget rather than a multiple of the full-size stage
   static constexpr int kSmemBytes = KD > 1 ? kSmemBudget + 2048 + kEpiBytes : kStages * kStageBytes + 2048 + kEpiBytes;
   static constexpr int kMaxStages = 24;  // barrier words stay well inside the 2 KB reserve
-  // pipeline depth when a stage holds only a_rows rows of A
+  // pipeline depth when a stage holds only a_rows rows of A.  The MMA still reads 128 rows (16 KB) from
+  // the start of every A slice, whatever a_rows is: with few rows and a narrow B tile that read runs past
+  // the end of its own stage, which is harmless inside the pipeline buffers but must not leave the
+  // shared-memory allocation from the last stage (an out-of-range shared address faults the kernel).
   static int stages_for(int a_rows) {
     if (a_rows >= 128 && KD == 1) return kStages;
     const int pool = KD > 1 ? kSmemBudget : kStages * kStageBytes;
-    const int n = pool / (kStageBytes - (128 - a_rows) * 128 * KD);
+    const int stage = kStageBytes - (128 - a_rows) * 128 * KD;
+    int n = pool / stage;
+    while (n > 1 && (n - 1) * stage + (KD - 1) * a_rows * 128 + 128 * 128 > pool) --n;
     return n > kMaxStages ? kMaxStages : n;
   }
   // TMEM columns
@@ -336,7 +341,7 @@ __device__ __forceinline__ void drain_cols(uint32_t taddr_row, int c0, int c1, c
 }
 
 // the same for a result that two issuing threads accumulated in two places: columns [0, c1) of the
-// accumulator at taddr_row plus the same columns `other` columns further on (fp32 kinds)
+// accumulator at taddr_row plus the same columns `other` columns further on
 template <MmaKind KIND, int EPI>
 __device__ __forceinline__ void drain_cols_sum2(uint32_t taddr_row, uint32_t other, int c1, const GemmArgs& g, int row,
                                                 int ncol0, float sa, void* rowptr) {
@@ -346,7 +351,10 @@ __device__ __forceinline__ void drain_cols_sum2(uint32_t taddr_row, uint32_t oth
     tmem_ld32(taddr_row + other + c, q);
     tc_wait_ld();
 #pragma unroll
-    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
+    for (int i = 0; i < 32; ++i) {
+      if constexpr (KIND == MmaKind::I8) r[i] += q[i];  // int32 accumulators: exact in any order
+      else r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
+    }
     store_cols<KIND, EPI, 32>(r, g, row, ncol0 + c, sa, rowptr);
   }
 }

@@ -290,7 +290,7 @@ int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw
 int gnk_debug_force_tile(int sel);
 int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default (staged), 0 direct stores from registers, 1 bulk tensor stores through shared-memory staging */
 int gnk_debug_max_clusters(int n);
-int gnk_debug_deep_stage(int on); /* 64-wide tile of the block-scaled GEMMs: 1 (default) = four 128-byte K slices per pipeline stage where the shape qualifies (one tile per CTA, K bytes a multiple of 128 and >= 2048), 0 = always one */
+int gnk_debug_deep_stage(int on); /* 64-wide GEMM tile: 1 (default) = four 128-byte K slices per pipeline stage where the shape qualifies (one tile per CTA, K bytes a multiple of 128 and >= 2048), 0 = always one */
 int gnk_debug_trace(void* device_buffer);
 int gnk_debug_attn_trace(void* device_buffer); /* attention: clock stamps of CTA 0, 2 tiles x 32 key tiles x 8 int64 (NULL = off) */
 /* GEMM + reduce-scatter: per-CTA timeline into a caller-owned, caller-zeroed device buffer of 160 x 8

@@ -321,6 +321,40 @@ def test_mxfp8_skinny_decode_shapes(gk, M):
     assert_parity(out, ref)
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 2048, 4096), (100, 1024, 4096 + 384), (128, 4096 + 64, 8192), (8, 512, 6144 + 128)])
+def test_skinny_dense_kinds_deep_stages(gk, M, N, K):
+    """The same pipeline for the kinds without block scales: INT8 stays exact (int32 sums in any order),
+    FP8 row-scaled and BF16 stay within the parity bound and within one output step of the one-slice pipeline."""
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    A8, B8 = rand_i8((M, K), 71), rand_i8((N, K), 72)
+    g = torch.Generator().manual_seed(73)
+    sA, sB = torch.randn(M, 1, generator=g).div(128), torch.randn(1, N, generator=g).div(128)
+    Ab, Bb = randn_bf16((M, K), 74, "cpu"), randn_bf16((N, K), 75, "cpu")
+    Af, sAf = gk.quantize_rowwise(Ab.cuda(), torch.float8_e4m3fn)
+    Bf, sBf = gk.quantize_rowwise(Bb.cuda(), torch.float8_e4m3fn)
+
+    def run():
+        return (gk.triton_mm(A8.cuda(), B8.cuda().T), gk.triton_mm(A8.cuda(), B8.cuda().T, scale_A=sA.cuda(), scale_B=sB.cuda()),
+                gk.triton_mm(Af, Bf.T, scale_A=sAf.view(M, 1), scale_B=sBf.view(1, N)), gk.triton_mm(Ab.cuda(), Bb.cuda().T))
+
+    try:
+        assert L.gnk_debug_force_tile(3) == 0
+        deep = run()
+        assert L.gnk_debug_deep_stage(0) == 0
+        one = run()
+    finally:
+        L.gnk_debug_deep_stage(1)
+        L.gnk_debug_force_tile(-1)
+    assert torch.equal(deep[0].cpu(), omm.int8_mm_exact(A8, B8))
+    assert torch.equal(deep[1].cpu(), omm.mm_i8_row_scaled(A8, B8, sA, sB))
+    assert torch.equal(deep[0], one[0]) and torch.equal(deep[1], one[1])
+    assert_parity(deep[3], omm.mm_bf16(Ab, Bb))
+    for d, o in ((deep[2], one[2]), (deep[3], one[3])):
+        assert float((d.float() - o.float()).abs().max()) <= 2.0**-7 * float(o.float().abs().max())
+
+
 @pytest.mark.parametrize("kind", ["mxfp8", "nvfp4"])
 @pytest.mark.parametrize("M,N,K", [(16, 2048, 4096), (100, 1024, 4096 + 384), (128, 4096 + 64, 8192), (8, 512, 6144 + 128)])
 def test_skinny_four_k_slices_per_stage(gk, kind, M, N, K):
