@@ -13,6 +13,11 @@
 //   warps 10-11 idle: they complete the warpgroup that hands its registers to the promotion warps
 //              (setmaxnreg: 224 for warps 0-7, 56 for the rest)
 // Persistent CTAs over 128 x 256 output tiles.  All barrier waits are bounded.
+// Tried and measured slower at 8192^3: 128 x 192 tiles with TWELVE promotion warps (warp = 32 rows x 64 columns,
+// one 64-column TMEM read per K block instead of two, buffer released before the FMAs, 152 registers): 1251
+// TFLOP/s against 1644 for this layout, 1318 cycles per K block against 1113.  A K block costs about what the
+// tcgen05.ld of its accumulator columns costs (128 KB here at ~120 bytes per clock), however the reads are
+// spread over warps: the TMEM read path, not the round-trip latency of one warp, is the limit.
 #include "gnk_common.cuh"
 
 namespace gnk {
