@@ -62,6 +62,7 @@ _SIGNATURES = {
     "gnk_debug_max_clusters": (c_int, [c_int]),
     "gnk_debug_trace": (c_int, [_P]),
     "gnk_debug_deep_stage": (c_int, [c_int]),
+    "gnk_debug_stage_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int32)]),
 }
 
 

@@ -316,6 +316,53 @@ extern "C" int gnk_debug_staged(int mode) {
   return GNK_OK;
 }
 
+// Host-side pipeline plan of one kernel configuration, for tests of the shared-memory arithmetic:
+// out[0] = stages, out[1] = bytes per stage, out[2] = bytes the stages may use, out[3] = bytes from the start of
+// the LAST stage to the end of the 128-row read the MMA makes from its last A slice (must be <= out[2] + the part
+// of the last stage in front of it, i.e. (stages - 1) * out[1] + out[3] <= out[2]).
+// kind: 0 bf16/fp16, 1 int8, 2 fp8, 3 mxfp8, 4 nvfp4; tile as in gnk_debug_force_tile; kd = K slices per stage.
+namespace {
+template <MmaKind KIND, int BN, int CG, int KD>
+int stage_plan(int a_rows, int32_t* out) {
+  using C = Cfg<KIND, BN, CG, EPI_BF16, 1, KD>;
+  const int stage = C::kStageBytes - (128 - a_rows) * 128 * KD;
+  out[0] = C::stages_for(a_rows);
+  out[1] = stage;
+  out[2] = KD > 1 ? C::kSmemBudget : C::kStages * C::kStageBytes;
+  out[3] = (KD - 1) * a_rows * 128 + 128 * 128;
+  return GNK_OK;
+}
+template <MmaKind KIND>
+int stage_plan_kind(int tile, int kd, int a_rows, int32_t* out) {
+  if (kd == 1) {
+    switch (tile) {
+      case 0: return stage_plan<KIND, 256, 2, 1>(a_rows, out);
+      case 1: return stage_plan<KIND, 256, 1, 1>(a_rows, out);
+      case 2: return stage_plan<KIND, 128, 1, 1>(a_rows, out);
+      case 3: return stage_plan<KIND, 64, 1, 1>(a_rows, out);
+      case 4: return stage_plan<KIND, 192, 2, 1>(a_rows, out);
+    }
+  } else if (tile == 3 && kd == 2) {
+    return stage_plan<KIND, 64, 1, 2>(a_rows, out);
+  } else if (tile == 3 && kd == 4) {
+    return stage_plan<KIND, 64, 1, 4>(a_rows, out);
+  }
+  return GNK_ERR_BAD_ARG;
+}
+}  // namespace
+
+extern "C" int gnk_debug_stage_plan(int kind, int tile, int kd, int a_rows, int32_t* out) {
+  if (!out || a_rows < 8 || a_rows > 128 || a_rows % 8) return GNK_ERR_BAD_ARG;
+  switch (kind) {
+    case 0: return stage_plan_kind<MmaKind::F16>(tile, kd, a_rows, out);
+    case 1: return stage_plan_kind<MmaKind::I8>(tile, kd, a_rows, out);
+    case 2: return stage_plan_kind<MmaKind::F8F6F4>(tile, kd, a_rows, out);
+    case 3: return stage_plan_kind<MmaKind::MXF8F6F4>(tile, kd, a_rows, out);
+    case 4: return stage_plan_kind<MmaKind::MXF4NVF4>(tile, kd, a_rows, out);
+  }
+  return GNK_ERR_BAD_ARG;
+}
+
 extern "C" int gnk_debug_max_clusters(int n) {
   g_max_clusters = n < 0 ? 0 : n;
   return GNK_OK;

@@ -290,6 +290,11 @@ int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw
 int gnk_debug_force_tile(int sel);
 int gnk_debug_staged(int mode); /* pair-tile epilogue: -1 default (staged), 0 direct stores from registers, 1 bulk tensor stores through shared-memory staging */
 int gnk_debug_max_clusters(int n);
+/* Host-side pipeline plan of a GEMM configuration (no GPU needed): kind 0 bf16/fp16, 1 int8, 2 fp8, 3 mxfp8,
+ * 4 nvfp4; tile as in gnk_debug_force_tile; kd = 128-byte K slices per stage (1, or 2 / 4 with tile 3); a_rows =
+ * rows of A kept per stage (8..128).  out[0] = stages, out[1] = bytes per stage, out[2] = bytes the stages may use,
+ * out[3] = bytes from the start of the last stage to the end of the 128-row operand read of its last A slice. */
+int gnk_debug_stage_plan(int kind, int tile, int kd, int a_rows, int32_t* out);
 int gnk_debug_deep_stage(int on); /* 64-wide GEMM tile: 1 (default) = four 128-byte K slices per pipeline stage where the shape qualifies (one tile per CTA, K bytes a multiple of 128 and >= 2048), 0 = always one */
 int gnk_debug_trace(void* device_buffer);
 int gnk_debug_attn_trace(void* device_buffer); /* attention: clock stamps of CTA 0, 2 tiles x 32 key tiles x 8 int64 (NULL = off) */

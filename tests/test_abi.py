@@ -92,3 +92,26 @@ def test_gemm_rs_pull_entry_refuses_a_missing_multicast_address():
     arr = (ctypes.c_void_p * 2)(p, p)
     rc = L.gnk_gemm_rs_bf16_pull(p, 64, p, 64, arr, ctypes.c_void_p(0), arr, p, 256, 512, 256, 64, 0, 2, 0, 0, ctypes.c_void_p(0))
     assert rc == _lib.ERR_BAD_ARG
+
+
+def test_pipeline_plan_keeps_the_operand_read_inside_shared_memory():
+    """A problem with fewer than 128 rows keeps only `a_rows` rows of A per pipeline stage, but the MMA
+    still reads 128 rows (16 KB) from the start of every A slice.  From the last stage that read must
+    end inside the bytes the stages own (an out-of-range shared address faults the kernel): for every
+    kind, tile and stage depth the plan the launcher uses satisfies
+    (stages - 1) * stage_bytes + tail <= pool."""
+    from gn_kernels_b200 import _lib
+
+    L = _lib.lib()
+    out = (ctypes.c_int32 * 4)()
+    combos = [(0, 1), (1, 1), (2, 1), (3, 1), (4, 1), (3, 2), (3, 4)]
+    for kind in range(5):
+        for tile, kd in combos:
+            for a_rows in range(8, 129, 8):
+                assert L.gnk_debug_stage_plan(kind, tile, kd, a_rows, out) == 0
+                stages, stage_bytes, pool, tail = list(out)
+                assert stages >= 2, (kind, tile, kd, a_rows, stages)
+                assert stages * stage_bytes <= pool
+                assert (stages - 1) * stage_bytes + tail <= pool, (kind, tile, kd, a_rows, list(out))
+                assert stage_bytes % 1024 == 0 or kind >= 3  # operand slices stay 1024-byte aligned (scale atoms follow them)
+    assert L.gnk_debug_stage_plan(0, 7, 1, 16, out) != 0 and L.gnk_debug_stage_plan(0, 3, 4, 12, out) != 0
