@@ -250,7 +250,7 @@ int dispatch_tile(const void* A, int64_t lda, const void* Bt, int64_t ldb, const
         const int64_t k_bytes = K * ElemInfo<KIND>::kNum / ElemInfo<KIND>::kDen;
         const int64_t tiles = ((M + 127) / 128) * ((N + 63) / 64);
         // (not with an fp16 accumulator: the two issuing threads' partial sums are added as fp32 words)
-        if (g_deep_stage.load() != 0 && !(g.f16 & 2) && k_bytes % 128 == 0 && k_bytes >= 2048 && tiles <= num_sms()) {
+        if (g_deep_stage.load() != 0 && !(g.f16 & 2) && k_bytes % 128 == 0 && k_bytes >= 1024 && tiles <= num_sms()) {
           // the rows of A share the stage with the weight slices: few rows leave room for four slices
           // per stage, more rows for two (the bytes of B in flight are what hides the DRAM latency)
           if (M <= 32) return launch<KIND, 64, 1, EPI, 1, 4>(A, lda, Bt, ldb, SFA, SFB, g, M, N, K, st);
