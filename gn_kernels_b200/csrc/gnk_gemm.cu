@@ -30,6 +30,7 @@ namespace {
 using namespace gnk::gemm;
 
 std::atomic<long long*> g_trace{nullptr};  // test hook (gnk_debug_trace): device buffer of 2*2*256*3 + 4 int64
+std::atomic<int> g_pdl{1};           // test hook (gnk_debug_deep_stage bit 1 clear = no programmatic dependent launch)
 std::atomic<int> g_max_clusters{0};  // test hook (gnk_debug_max_clusters): cap on the persistent grid, 0 = none
 
 template <MmaKind KIND>
@@ -131,7 +132,25 @@ int launch(const void* A, int64_t lda, const void* Bt, int64_t ldb, const uint8_
   } else {
     maps.c = tm_a;
   }
-  kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, maps, g);
+  if constexpr (KD > 1) {
+    // Decode-shaped problems are short kernels issued back to back (one per layer): launched with
+    // programmatic stream serialization, the next kernel's CTAs may start their set-up (barriers, TMEM,
+    // descriptor prefetch) while this one drains; every such kernel waits for its predecessors
+    // (griddepcontrol.wait) before it touches global memory, so the stream order of all data is kept.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * CG));
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    GNK_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_sfa, tm_sfb, maps, g));
+  } else {
+    kern<<<clusters * CG, 192, C::kSmemBytes, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, maps, g);
+  }
   GNK_LAUNCH_OK();
   return GNK_OK;
 }
@@ -306,7 +325,8 @@ extern "C" int gnk_debug_trace(void* device_buffer) {
 // Debug: 0 = the 64-wide tile always moves one 128-byte K slice per stage, 1 (default) = four slices per
 // stage where the shape qualifies.
 extern "C" int gnk_debug_deep_stage(int on) {
-  g_deep_stage = on;
+  g_deep_stage = on & 1;
+  g_pdl = (on & 2) ? 0 : 1;  // bit 1: launch the deep-stage kernels without programmatic stream serialization
   return GNK_OK;
 }
 

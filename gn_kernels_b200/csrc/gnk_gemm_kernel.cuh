@@ -632,6 +632,12 @@ __global__ void __cluster_dims__(CG, 1, 1) __launch_bounds__(EPI == EPI_RS ? 320
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  if constexpr (KD > 1) {
+    // launched with programmatic stream serialization: the set-up above may have run under the previous
+    // kernel's tail; let the next kernel start its own, then wait for everything this one depends on
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
   unsigned long long* rs_tr = nullptr;
   if constexpr (EPI == EPI_RS) {
     if (g.rs.trace) {

@@ -295,7 +295,7 @@ int gnk_debug_max_clusters(int n);
  * rows of A kept per stage (8..128).  out[0] = stages, out[1] = bytes per stage, out[2] = bytes the stages may use,
  * out[3] = bytes from the start of the last stage to the end of the 128-row operand read of its last A slice. */
 int gnk_debug_stage_plan(int kind, int tile, int kd, int a_rows, int32_t* out);
-int gnk_debug_deep_stage(int on); /* 64-wide GEMM tile: 1 (default) = four 128-byte K slices per pipeline stage where the shape qualifies (one tile per CTA, K bytes a multiple of 128 and >= 1024), 0 = always one */
+int gnk_debug_deep_stage(int on); /* 64-wide GEMM tile: bit 0: 1 (default) = four 128-byte K slices per pipeline stage where the shape qualifies (one tile per CTA, K bytes a multiple of 128 and >= 1024), 0 = always one; bit 1 set: launch those kernels without programmatic stream serialization */
 int gnk_debug_trace(void* device_buffer);
 int gnk_debug_attn_trace(void* device_buffer); /* attention: clock stamps of CTA 0, 2 tiles x 32 key tiles x 8 int64 (NULL = off) */
 /* GEMM + reduce-scatter: per-CTA timeline into a caller-owned, caller-zeroed device buffer of 160 x 8

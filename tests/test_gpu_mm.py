@@ -355,6 +355,33 @@ def test_skinny_dense_kinds_deep_stages(gk, M, N, K):
         assert float((d.float() - o.float()).abs().max()) <= 2.0**-7 * float(o.float().abs().max())
 
 
+def test_back_to_back_dependent_decode_gemms(gk):
+    """The decode-shaped kernels are launched with programmatic stream serialization: the next kernel's
+    set-up may run under the previous one's tail, but it must not read or write global memory before its
+    predecessor has finished.  A chain in which every GEMM consumes the previous one's output (and the
+    last overwrites the first's input buffer) gives the same bits as the same chain with a host
+    synchronisation after every launch."""
+    M, D = 16, 4096
+    g = torch.Generator().manual_seed(81)
+    x0 = (torch.randn(M, D, generator=g)).bfloat16().cuda()
+    Ws = [(torch.randn(D, D, generator=g) / D**0.5).bfloat16().cuda() for _ in range(4)]
+
+    def chain(sync):
+        x = x0.clone()
+        for rep in range(3):
+            for W in Ws:
+                x = gk.cutedsl.sm100.sm100_mm_bf16.mm(x, W.T)
+                if sync:
+                    torch.cuda.synchronize()
+        return x
+
+    ref = chain(True)
+    for _ in range(5):
+        assert torch.equal(chain(False), ref)
+    # and against the oracle for the first link
+    assert_parity(gk.cutedsl.sm100.sm100_mm_bf16.mm(x0, Ws[0].T), omm.mm_bf16(x0.cpu(), Ws[0].cpu()))
+
+
 @pytest.mark.parametrize("kind", ["mxfp8", "nvfp4"])
 @pytest.mark.parametrize("M,N,K", [(16, 2048, 4096), (100, 1024, 4096 + 384), (128, 4096 + 64, 8192), (8, 512, 6144 + 128)])
 def test_skinny_four_k_slices_per_stage(gk, kind, M, N, K):
