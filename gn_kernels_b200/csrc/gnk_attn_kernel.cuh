@@ -282,9 +282,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr uint32_t kIdescO = idesc_dense(kOAcc16 ? 0u : 1u, kVFmt, kVFmt, kBM, kD, 0, 1);  // B (= V) N-major
     bool ok = n_max > 0 && mbar_wait(bar_q, 0, (0x12u << 24) | (1u << 16));
     // S_T(j) = Q_T K_j^T.  The K stage is released by the last tile that reads it.
-    auto issue_s = [&](int t, int j) -> bool {
+    // waits for K_j; done ahead of the wait for P wherever possible: a barrier wait costs ~100 cycles even
+    // when its phase has long completed, and everything after P is ready sits on the tile's critical path
+    auto wait_k = [&](int j) -> bool {
+      return mbar_wait(bar_kfull(j % kStages), (j / kStages) & 1, (0x12u << 24) | (2u << 16) | j);
+    };
+    auto issue_s = [&](int t, int j, bool k_waited) -> bool {
       const int st = j % kStages;
-      if (!mbar_wait(bar_kfull(st), (j / kStages) & 1, (0x12u << 24) | (2u << 16) | j)) return false;
+      if (!k_waited && !wait_k(j)) return false;
       tc_fence_after();
       const uint32_t q_addr = sm_q + t * kQBytes, k_addr = sm_k + st * kKBytes;
       const uint32_t d = tmem_base + t * kBN;
@@ -314,19 +319,21 @@ __global__ void __launch_bounds__(kThreads, 1)
     // O_T += P_T(j) V_j.  P is read from TMEM (the first 64 columns of the tile's score region).
     auto issue_pv = [&](int t, int j) -> bool {
       const int st = j % kStages;
-      if (!mbar_wait(bar_pready(t), j & 1, (0x12u << 24) | (4u << 16) | j)) return false;
+      // V_j first (it landed long ago), P_t(j) last: nothing but the issue itself follows the moment P is ready
       if (!mbar_wait(bar_vfull(st), (j / kStages) & 1, (0x12u << 24) | (5u << 16) | j)) return false;
-      tc_fence_after();
       const uint32_t p_tmem = tmem_base + t * kBN;
       const uint32_t v_addr = sm_v + st * kVBytes;
       const uint32_t d = tmem_base + 256 + t * kD;
       const bool last_user = (t == 1) || (j >= n_t[1]);
+      const uint64_t v_desc0 = sdesc_mn128(v_addr, kVHalfBytes);
+      if (!mbar_wait(bar_pready(t), j & 1, (0x12u << 24) | (4u << 16) | j)) return false;
+      tc_fence_after();
       if (leader) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          // A: 16 key columns of P = 8 TMEM columns; B: 16 key rows of V (N-major, both 64-column halves)
-          const uint64_t v_desc = sdesc_mn128(v_addr + kk * 16 * 128, kVHalfBytes);
-          tc_mma_f16_ts(d, p_tmem + kk * 8, v_desc, kIdescO, (j | kk) != 0);
+          // A: 16 key columns of P = 8 TMEM columns; B: 16 key rows of V (N-major, both 64-column halves):
+          // 16 rows of 128 bytes further on per step (the address field counts 16-byte units)
+          tc_mma_f16_ts(d, p_tmem + kk * 8, v_desc0 + kk * ((16 * 128) >> 4), kIdescO, (j | kk) != 0);
         }
         if (last_user) tc_commit<1>(bar_vempty(st));
         tc_commit<1>(bar_pvdone(t));
@@ -334,14 +341,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       return true;
     };
-    if (ok && n_t[0] > 0) ok = issue_s(0, 0);
-    if (ok && n_t[1] > 0) ok = issue_s(1, 0);
+    if (ok && n_t[0] > 0) ok = issue_s(0, 0, false);
+    if (ok && n_t[1] > 0) ok = issue_s(1, 0, false);
     for (int j = 0; j < n_max && ok; ++j) {
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (!ok || j >= n_t[t]) continue;
-        ok = issue_pv(t, j);                                  // needs P_t(j): the softmax of tile t has consumed S_t(j)
-        if (ok && j + 1 < n_t[t]) ok = issue_s(t, j + 1);     // executes after P_t(j) has been read (in-order pipe)
+        const bool has_next = j + 1 < n_t[t];
+        if (has_next) ok = wait_k(j + 1);                     // ahead of the wait for P
+        if (ok) ok = issue_pv(t, j);                          // needs P_t(j): the softmax of tile t has consumed S_t(j)
+        if (ok && has_next) ok = issue_s(t, j + 1, true);     // executes after P_t(j) has been read (in-order pipe)
       }
     }
   }
