@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto bar_sfull = [&](int t) { return bars + 8 * (1 + 4 * kStages + t); };    // per query tile
   auto bar_pready = [&](int t) { return bars + 8 * (3 + 4 * kStages + t); };
   auto bar_pvdone = [&](int t) { return bars + 8 * (5 + 4 * kStages + t); };
-  const uint32_t tmem_slot = bars + 8 * (7 + 4 * kStages);
+  auto bar_sread = [&](int t) { return bars + 8 * (7 + 4 * kStages + t); };    // the tile's score row is in registers
+  const uint32_t tmem_slot = bars + 8 * (9 + 4 * kStages);
   float* sk_ptr = reinterpret_cast<float*>(smem_raw + (sm_sk - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -221,6 +222,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_sfull(s), 1);
       mbar_init(bar_pready(s), 4);  // one arrival per softmax warp of the tile
       mbar_init(bar_pvdone(s), 1);
+      mbar_init(bar_sread(s), 4);   // one arrival per softmax warp of the tile
     }
     fence_mbar_init();
   }
@@ -287,12 +289,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     auto wait_k = [&](int j) -> bool {
       return mbar_wait(bar_kfull(j % kStages), (j / kStages) & 1, (0x12u << 24) | (2u << 16) | j);
     };
-    auto issue_s = [&](int t, int j, bool k_waited) -> bool {
+    // `part`: 0 = all 128 key columns; 1 = key columns 64..127 only, without signalling (they do not overlap P,
+    // which sits in score columns 0..63, so they may be computed while the softmax of the previous key tile
+    // still runs, as soon as that softmax has its score row in registers); 2 = key columns 0..63, which must
+    // follow the P V product that reads P, then the signals for the whole tile.
+    constexpr uint32_t kIdescSHalf = (kIdescS & ~(0x3Fu << 17)) | ((64u >> 3) << 17);
+    auto issue_s = [&](int t, int j, bool k_waited, int part) -> bool {
       const int st = j % kStages;
       if (!k_waited && !wait_k(j)) return false;
       tc_fence_after();
-      const uint32_t q_addr = sm_q + t * kQBytes, k_addr = sm_k + st * kKBytes;
-      const uint32_t d = tmem_base + t * kBN;
+      const int key0 = part == 1 ? 64 : 0;  // first key row / score column of this part
+      const uint32_t q_addr = sm_q + t * kQBytes, k_addr = sm_k + st * kKBytes + key0 * 128;
+      const uint32_t d = tmem_base + t * kBN + key0;
+      const uint32_t idesc = part == 0 ? kIdescS : kIdescSHalf;
       const bool last_user = (t == 1) || (j >= n_t[1]);
       if (leader) {
         if constexpr (kQk16) {
@@ -300,18 +309,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int kk = 0; kk < 8; ++kk) {  // 16 elements of D per step, half kk / 4
             const uint64_t q_desc = sdesc_k128(q_addr + (kk >> 2) * (kBM * 128)) + 2 * (kk & 3);
             const uint64_t k_desc = sdesc_k128(k_addr + (kk >> 2) * (kBN * 128)) + 2 * (kk & 3);
-            tc_mma<MmaKind::F16, 1>(d, q_desc, k_desc, kIdescS, kk != 0);
+            tc_mma<MmaKind::F16, 1>(d, q_desc, k_desc, idesc, kk != 0);
           }
         } else {
           const uint64_t q_desc = sdesc_k128(q_addr), k_desc = sdesc_k128(k_addr);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            if constexpr (QK == kQkInt8) tc_mma<MmaKind::I8, 1>(d, q_desc + 2 * kk, k_desc + 2 * kk, kIdescS, kk != 0);
-            else tc_mma<MmaKind::F8F6F4, 1>(d, q_desc + 2 * kk, k_desc + 2 * kk, kIdescS, kk != 0);
+            if constexpr (QK == kQkInt8) tc_mma<MmaKind::I8, 1>(d, q_desc + 2 * kk, k_desc + 2 * kk, idesc, kk != 0);
+            else tc_mma<MmaKind::F8F6F4, 1>(d, q_desc + 2 * kk, k_desc + 2 * kk, idesc, kk != 0);
           }
         }
-        if (last_user) tc_commit<1>(bar_kempty(st));
-        tc_commit<1>(bar_sfull(t));
+        if (part != 1) {
+          if (last_user) tc_commit<1>(bar_kempty(st));
+          tc_commit<1>(bar_sfull(t));
+        }
       }
       __syncwarp();
       return true;
@@ -341,16 +352,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       return true;
     };
-    if (ok && n_t[0] > 0) ok = issue_s(0, 0, false);
-    if (ok && n_t[1] > 0) ok = issue_s(1, 0, false);
+    if (ok && n_t[0] > 0) ok = issue_s(0, 0, false, 0);
+    if (ok && n_t[1] > 0) ok = issue_s(1, 0, false, 0);
     for (int j = 0; j < n_max && ok; ++j) {
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (!ok || j >= n_t[t]) continue;
         const bool has_next = j + 1 < n_t[t];
-        if (has_next) ok = wait_k(j + 1);                     // ahead of the wait for P
+        if (has_next) {
+          // K_(j+1) and "S_t(j) is in registers" come long before P_t(j): the upper half of S_t(j+1) runs meanwhile
+          ok = wait_k(j + 1) && mbar_wait(bar_sread(t), j & 1, (0x12u << 24) | (6u << 16) | j);
+          if (ok) ok = issue_s(t, j + 1, true, 1);
+        }
         if (ok) ok = issue_pv(t, j);                          // needs P_t(j): the softmax of tile t has consumed S_t(j)
-        if (ok && has_next) ok = issue_s(t, j + 1, true);     // executes after P_t(j) has been read (in-order pipe)
+        if (ok && has_next) ok = issue_s(t, j + 1, true, 2);  // executes after P_t(j) has been read (in-order pipe)
       }
     }
   }
@@ -414,7 +429,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, raw[c]);
       tc_wait_ld();
-      // from here on the score region may be overwritten with P
+      // from here on the score region may be overwritten: columns 64..127 by the next key tile's scores
+      // (the MMA warp waits for this signal), columns 0..63 with P
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sread(t));
       float x[4][32];
       // independent partial maxima / sums per 32-column chunk: one serial chain over the whole row
       // would cost ~4 cycles per link and is exactly what a latency-bound softmax thread cannot afford
