@@ -30,6 +30,12 @@
 // scheduler instead of two, row maxima exchanged through shared memory): correct, 669 / 764 TFLOP/s:
 // at the 112 registers such a thread can have it spills, and the extra warps contend instead of
 // filling each other's stalls.
+// And so was one MMA issuer warp PER query tile (each blocking on its own tile's barriers only; K / V stages
+// handed back by two arrivals), with or without the P V product split into two halves of 64 keys (the first
+// issued half-way through the softmax's second pass): correct, 772 TFLOP/s causal against 865-877.  The
+// single issuer that serves the tiles strictly in turn is what keeps the two softmax groups in anti-phase;
+// with independent issuers they drift into phase and then share the tensor pipe and the special-function
+// unit at the same moments.
 // Every barrier wait is bounded (see mbar_wait); a softmax warp whose wait runs out stops waiting
 // but keeps arriving at the barriers of its group, so the CTA always reaches its end.
 #pragma once
