@@ -18,6 +18,12 @@
 // CG = 2 pairs two CTAs (a cluster) on a 256 x BN tile: each loads its 128 rows of A and
 // its half of B, CTA 0 issues cta_group::2 MMAs for both, and completion is multicast to
 // the barriers of both CTAs.  No TMA load here uses cluster multicast.
+// Decode-shaped problems (one 128 x 64 tile per CTA, at least 1 KB of K per row) take a variant of the
+// same template with 4 or 2 128-byte K slices per pipeline stage (rank-3 TMA boxes) and TWO issuing
+// threads (warp 5 and warp 3, which is idle until its epilogue), each with an accumulator of its own that
+// the epilogue adds: at these shapes the per-stage cost of the producer and issuer loops, not bytes or
+// math, sets the pace.  These kernels are launched with programmatic stream serialization and wait for
+// their predecessors (griddepcontrol.wait) before their first global access.
 // Every barrier wait is bounded; a wait that runs out sets the device status word and the
 // role leaves its loop, after which the CTA tears down normally.
 #include <atomic>
