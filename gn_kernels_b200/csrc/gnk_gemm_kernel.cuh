@@ -66,6 +66,10 @@ struct GemmArgs {
     // Pull variant: the multicast address of the ranks' [M, N] partial buffers (staging[] are then the
     // same buffers seen per rank).  Null selects the push variant.
     const __nv_bfloat16* mc_partial;
+    // All-reduce variant (pull only): the multicast address of the ranks' [M, N] output buffers.  The owner
+    // then stores every reduced piece through it (one multimem.st reaches all ranks) instead of into `out`,
+    // so every rank ends with all M rows.  Null = reduce-scatter.
+    __nv_bfloat16* mc_out;
     // debug: 8 words per CTA (globaltimer ns): start, epilogue end, reducer end, reducer wait total,
     // MMA end, epilogue store+signal total, epilogue wait-for-accumulator total (null = off)
     unsigned long long* trace;
@@ -421,6 +425,19 @@ __device__ __forceinline__ void reduce_chunk_multimem(const GemmArgs& g, int lr0
                  : "=r"(v[q].x), "=r"(v[q].y), "=r"(v[q].z), "=r"(v[q].w)
                  : "l"(src)
                  : "memory");
+  }
+  if (g.rs.mc_out) {
+    // all-reduce: this rank's rows of the result go to every rank's output in one store through the switch
+#pragma unroll
+    for (int q = 0; q < PB; ++q) {
+      __nv_bfloat16* dst =
+          g.rs.mc_out + (static_cast<int64_t>(g.rs.rank) * g.rs.rows_per_owner + rr[q]) * g.rs.ldo + cc[q];
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                   "f"(__uint_as_float(v[q].x)), "f"(__uint_as_float(v[q].y)), "f"(__uint_as_float(v[q].z)),
+                   "f"(__uint_as_float(v[q].w))
+                   : "memory");
+    }
+    return;
   }
 #pragma unroll
   for (int q = 0; q < PB; ++q)

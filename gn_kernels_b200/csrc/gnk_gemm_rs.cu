@@ -164,7 +164,7 @@ extern "C" int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, i
 namespace {
 int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging, const void* multicast,
                  int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N, int64_t K_local, int rank,
-                 int world, uint32_t timeout_ms, int lagged_exit, gnk_stream_t stream) {
+                 int world, uint32_t timeout_ms, int lagged_exit, gnk_stream_t stream, void* output_multicast = nullptr) {
   if (!x || !w || !output || M <= 0 || N <= 0 || K_local <= 0) return GNK_ERR_BAD_ARG;
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return GNK_ERR_BAD_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(output)) return GNK_ERR_BAD_ALIGN;
@@ -197,6 +197,7 @@ int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c
     g.rs.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
   }
   g.rs.mc_partial = static_cast<const __nv_bfloat16*>(multicast);
+  g.rs.mc_out = static_cast<__nv_bfloat16*>(output_multicast);
   g.rs.out = static_cast<__nv_bfloat16*>(output);
   g.rs.ldo = ldo;
   if (p.cg == 2) return launch_rs<256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
@@ -219,4 +220,19 @@ extern "C" int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, 
   if (world > 1 && (!partial_multicast || !aligned16(partial_multicast))) return GNK_ERR_BAD_ARG;
   return gemm_rs_impl(x, ldx, w, ldw, partial, partial_multicast, flags, output, ldo, M, N, K_local, rank, world,
                       timeout_ms, lagged_exit, stream);
+}
+
+// GEMM + all-reduce: the pull variant whose owners store the reduced rows through the multicast address of
+// the ranks' [M, N] outputs, so every rank ends with the whole sum.  The exit barrier always waits: a rank's
+// output is complete only when every owner has finished.
+extern "C" int gnk_gemm_ar_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* partial,
+                                const void* partial_multicast, int32_t* const* flags, void* output,
+                                void* output_multicast, int64_t ldo, int64_t M, int64_t N, int64_t K_local, int rank,
+                                int world, uint32_t timeout_ms, gnk_stream_t stream) {
+  if (!output) return GNK_ERR_BAD_ARG;
+  if (world > 1 && (!partial_multicast || !aligned16(partial_multicast) || !output_multicast ||
+                    !aligned16(output_multicast)))
+    return GNK_ERR_BAD_ARG;
+  return gemm_rs_impl(x, ldx, w, ldw, partial, partial_multicast, flags, output, ldo, M, N, K_local, rank, world,
+                      timeout_ms, 0, stream, world > 1 ? output_multicast : nullptr);
 }

@@ -124,3 +124,54 @@ def gemm_rs(
             "gnk_gemm_rs_bf16",
         )
     return output
+
+
+def gemm_ar(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    partial: torch.Tensor,
+    partial_handle,
+    output: torch.Tensor,
+    output_handle,
+    flags: torch.Tensor,
+    flags_handle,
+    *,
+    timeout_ms: int = 0,
+) -> torch.Tensor:
+    """output[M, N] (on EVERY rank) = sum over ranks of bf16(x_r @ w_r^T), fp32 summation: the K-sharded GEMM
+    fused with an all-reduce.  Upstream has no such function; it is `gemm_rs` whose owners store the reduced
+    rows through the NVLink multicast address of the ranks' outputs instead of keeping them.
+
+    `partial`, `flags` as for `gemm_rs`; `output` is a symmetric-memory [M, N] bf16 buffer whose handle offers
+    a multicast address (NVSwitch systems), like `partial`."""
+    assert dist.is_initialized()
+    rank = dist.get_rank()
+    world = dist.get_world_size()
+    assert world <= 8
+    M, K = x.shape
+    N, _ = w.shape
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and output.dtype == torch.bfloat16
+    assert w.shape[1] == K and output.shape == (M, N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and output.is_contiguous()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    sp = fp = None
+    p_mc = o_mc = 0
+    if world > 1:
+        assert partial.dtype == torch.bfloat16 and flags.dtype == torch.int32
+        p_addr, p_mc = peer_addresses(partial, partial_handle, rank, world, M * N * 2)
+        _, o_mc = peer_addresses(output, output_handle, rank, world, M * N * 2)
+        f_addr, _ = peer_addresses(flags, flags_handle, rank, world, flag_words(M, N, world) * 4, align=4)
+        if not p_mc or not o_mc:
+            raise RuntimeError("gemm_ar needs symmetric-memory handles with a multicast address for `partial` and `output`")
+        sp = (ctypes.c_void_p * world)(*p_addr)
+        fp = (ctypes.c_void_p * world)(*f_addr)
+    with torch.cuda.device(x.device):
+        check(
+            lib().gnk_gemm_ar_bf16(
+                ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(w.data_ptr()), w.stride(0), sp,
+                ctypes.c_void_p(p_mc), fp, ctypes.c_void_p(output.data_ptr()), ctypes.c_void_p(o_mc), output.stride(0),
+                M, N, K, rank, world, timeout_ms, stream,
+            ),
+            "gnk_gemm_ar_bf16",
+        )
+    return output

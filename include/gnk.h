@@ -280,6 +280,16 @@ int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw
                           int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
                           int lagged_exit, gnk_stream_t stream);
 
+/* GEMM + all-reduce (no counterpart upstream, whose only fused collective is the reduce-scatter above): the
+ * same kernel and buffers as gnk_gemm_rs_bf16_pull, but the owner of a block of rows stores each reduced
+ * 16-byte piece through output_multicast, the NVLink multicast address of the ranks' [M, N] bf16 outputs
+ * (row pitch ldo), so after the call every rank holds all M rows of the sum.  `output` is this rank's own
+ * address of that buffer (world == 1: the plain GEMM writes there).  The exit barrier always waits. */
+int gnk_gemm_ar_bf16(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* partial,
+                     const void* partial_multicast, int32_t* const* flags, void* output, void* output_multicast,
+                     int64_t ldo, int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
+                     gnk_stream_t stream);
+
 /* ------------------------------------------------------------------ test hooks ---- */
 /* Process-wide switches for tests and profiling; none of them changes a result.
  * Force a GEMM tile configuration (0: 2-CTA 256x256, 1: 128x256, 2: 128x128, 3: 128x64, 4: 2-CTA 256x192 for

@@ -26,3 +26,9 @@ def gemm_rs(xs, ws, *, round_partials: bool = True):
         total = p if total is None else total + p
     rows = M // W
     return [total[r * rows : (r + 1) * rows].bfloat16() for r in range(W)]
+
+
+def gemm_ar(xs, ws, *, round_partials: bool = True):
+    """The all-reduce form of the same sum (no upstream function): every rank ends with all M rows,
+    i.e. the reduce-scatter outputs of all ranks stacked.  Returns one [M, N] bf16 tensor."""
+    return torch.cat(gemm_rs(xs, ws, round_partials=round_partials), dim=0)

@@ -28,6 +28,7 @@ def main():
     args = ap.parse_args()
     from gn_kernels_b200 import _lib
     from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import flag_words
+    from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import gemm_ar as _gemm_ar
     from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import gemm_rs as _gemm_rs
     from oracle import gemm_rs as ors
     from oracle.mm import max_rel_err
@@ -89,6 +90,29 @@ def main():
             assert int(flags.abs().sum()) == 0, "flags not restored to zero"
             dist.barrier()  # a faster peer's next call may signal this rank's flags as soon as it starts
         dist.barrier()
+
+        # GEMM + all-reduce (needs the multicast path): every rank ends with all rows of the sum
+        if bool(getattr(ph, "multicast_ptr", 0)) and mcast is not False:
+            full = symm_mem.empty(M, N, dtype=torch.bfloat16, device=dev)
+            oh = symm_mem.rendezvous(full, dist.group.WORLD)
+            for it in range(2):
+                full.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                _gemm_ar(x, w, partial, ph, full, oh, flags, fh, timeout_ms=args.timeout_ms)
+                torch.cuda.synchronize()
+                _lib.raise_on_device_error()
+                assert int(flags.abs().sum()) == 0, "flags not restored to zero after the all-reduce"
+                fulls = [torch.empty_like(full) for _ in range(W)]
+                dist.all_gather(fulls, full)
+                if rank == 0:
+                    want = ors.gemm_ar([t.cpu() for t in xs], [t.cpu() for t in ws])
+                    errs = [max_rel_err(f.cpu(), want) for f in fulls]
+                    same = all(torch.equal(f, fulls[0]) for f in fulls)
+                    ok = max(errs) <= 1e-2 and same
+                    print(f"gemm_ar W={W} M={M} N={N} K={Kl * W} call {it}: max rel err {max(errs):.2e} all ranks equal={same} {'OK' if ok else 'FAIL'}", flush=True)
+                    failures += 0 if ok else 1
+                dist.barrier()
 
         # A sequence with the exit wait deferred: four calls back to back with no host synchronisation in
         # between, the ranks deliberately out of step (each spins a different time first), then one
