@@ -55,6 +55,8 @@ _SIGNATURES = {
                                  c_int64, c_int, c_int, c_uint32, c_int, _P]),
     "gnk_gemm_rs_bf16_pull": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), _P, POINTER(c_void_p), _P, c_int64, c_int64,
                                       c_int64, c_int64, c_int, c_int, c_uint32, c_int, _P]),
+    "gnk_gemm_rs_f8": (c_int, [_P, c_int64, _P, c_int64, c_float, POINTER(c_void_p), _P, POINTER(c_void_p), _P, c_int64, c_int64,
+                               c_int64, c_int64, c_int, c_int, c_uint32, c_int, _P]),
     "gnk_gemm_ar_bf16": (c_int, [_P, c_int64, _P, c_int64, POINTER(c_void_p), _P, POINTER(c_void_p), _P, _P, c_int64, c_int64,
                                  c_int64, c_int64, c_int, c_int, c_uint32, _P]),
     "gnk_debug_attn_trace": (c_int, [_P]),

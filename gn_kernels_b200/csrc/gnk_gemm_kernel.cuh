@@ -275,7 +275,7 @@ __device__ __forceinline__ void finish_cols(const uint32_t* r, const GemmArgs& g
       if (g.scale_a) v = __fmul_rn(v, sa);
       if (g.scale_b) v = __fmul_rn(v, __ldg(g.scale_b + c));
       if (g.bias) v = __fadd_rn(v, __ldg(g.bias + c));
-    } else if constexpr (KIND == MmaKind::MXF4NVF4) {
+    } else if constexpr (KIND == MmaKind::MXF4NVF4 || (KIND == MmaKind::F8F6F4 && EPI == EPI_RS)) {
       v = __fmul_rn(v, g.alpha);
     }
     f[i] = v;

@@ -60,19 +60,23 @@ int make_plan(int64_t M, int64_t N, int world, RsPlan* p) {
   return GNK_OK;
 }
 
-template <int BN, int CG>
+// KIND: F16 (bf16 operands) or F8F6F4 (E4M3 operands, the partial product times g.alpha before its bf16 rounding)
+template <MmaKind KIND, int BN, int CG>
 int launch_rs(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g, int64_t M, int64_t N, int64_t K,
               cudaStream_t st) {
-  using C = Cfg<MmaKind::F16, BN, CG, EPI_RS>;
+  using C = Cfg<KIND, BN, CG, EPI_RS>;
+  constexpr bool kBf16 = KIND == MmaKind::F16;
+  constexpr int kElem = kBf16 ? 2 : 1;
+  const CUtensorMapDataType dt = kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUtensorMap tm_a, tm_b;
-  int rc = make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, M, K, ldx * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc = make_tmap_2d(&tm_a, dt, x, M, K, ldx * kElem, 128, 128 / kElem, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
-  rc = make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, w, N, K, ldw * 2, BN / CG, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_tmap_2d(&tm_b, dt, w, N, K, ldw * kElem, BN / CG, 128 / kElem, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != GNK_OK) return rc;
-  g.k_iters = static_cast<int>((K * 2 + 127) / 128);
+  g.k_iters = static_cast<int>((K * kElem + 127) / 128);
   g.a_rows = 128;
   g.stages = C::kStages;
-  auto kern = gemm_kernel<MmaKind::F16, BN, CG, EPI_RS>;
+  auto kern = gemm_kernel<KIND, BN, CG, EPI_RS>;
   static int resident[64];
   int dev = 0;
   GNK_CUDA_OK(cudaGetDevice(&dev));
@@ -164,16 +168,20 @@ extern "C" int64_t gnk_gemm_rs_plan(int64_t M, int64_t N, int world, int rank, i
 namespace {
 int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* const* staging, const void* multicast,
                  int32_t* const* flags, void* output, int64_t ldo, int64_t M, int64_t N, int64_t K_local, int rank,
-                 int world, uint32_t timeout_ms, int lagged_exit, gnk_stream_t stream, void* output_multicast = nullptr) {
+                 int world, uint32_t timeout_ms, int lagged_exit, gnk_stream_t stream, void* output_multicast = nullptr,
+                 bool fp8 = false, float alpha = 1.f) {
   if (!x || !w || !output || M <= 0 || N <= 0 || K_local <= 0) return GNK_ERR_BAD_ARG;
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return GNK_ERR_BAD_ARG;
   if (!aligned16(x) || !aligned16(w) || !aligned16(output)) return GNK_ERR_BAD_ALIGN;
-  if (K_local % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldo % 8 != 0) return GNK_ERR_BAD_SHAPE;
+  const int k_align = fp8 ? 16 : 8;  // 16-byte rows for TMA
+  if (K_local % k_align != 0 || ldx % k_align != 0 || ldw % k_align != 0 || ldo % 8 != 0) return GNK_ERR_BAD_SHAPE;
   int rc = check_arch();
   if (rc != GNK_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (world == 1)  // nothing to exchange: the GEMM writes the output rows itself
+  if (world == 1) {  // nothing to exchange: the GEMM writes the output rows itself
+    if (fp8) return GNK_ERR_UNSUPPORTED;  // the single-GPU FP8 entries take row scales, not one factor
     return gnk_mm_bf16(x, ldx, w, ldw, output, ldo, M, N, K_local, stream);
+  }
   if (!staging || !flags) return GNK_ERR_BAD_ARG;
   RsPlan p;
   rc = make_plan(M, N, world, &p);
@@ -183,7 +191,7 @@ int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c
   g.N = static_cast<int>(N);
   g.tiles_m = p.tiles_m;
   g.tiles_n = p.tiles_n;
-  g.alpha = 1.f;
+  g.alpha = alpha;
   g.vec_ok = 1;
   g.rs.world = world;
   g.rs.rank = rank;
@@ -200,8 +208,12 @@ int gemm_rs_impl(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c
   g.rs.mc_out = static_cast<__nv_bfloat16*>(output_multicast);
   g.rs.out = static_cast<__nv_bfloat16*>(output);
   g.rs.ldo = ldo;
-  if (p.cg == 2) return launch_rs<256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
-  return launch_rs<128, 1>(x, ldx, w, ldw, g, M, N, K_local, st);
+  if (fp8) {
+    if (p.cg == 2) return launch_rs<MmaKind::F8F6F4, 256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
+    return launch_rs<MmaKind::F8F6F4, 128, 1>(x, ldx, w, ldw, g, M, N, K_local, st);
+  }
+  if (p.cg == 2) return launch_rs<MmaKind::F16, 256, 2>(x, ldx, w, ldw, g, M, N, K_local, st);
+  return launch_rs<MmaKind::F16, 128, 1>(x, ldx, w, ldw, g, M, N, K_local, st);
 }
 }  // namespace
 
@@ -235,4 +247,15 @@ extern "C" int gnk_gemm_ar_bf16(const void* x, int64_t ldx, const void* w, int64
     return GNK_ERR_BAD_ARG;
   return gemm_rs_impl(x, ldx, w, ldw, partial, partial_multicast, flags, output, ldo, M, N, K_local, rank, world,
                       timeout_ms, 0, stream, world > 1 ? output_multicast : nullptr);
+}
+
+// The reduce-scatter with E4M3 operands and one dequantisation factor per rank (tensor-wise scales):
+// partial_r = bf16(alpha * (x_r w_r^T)) with fp32 accumulation.  partial_multicast null = push variant.
+extern "C" int gnk_gemm_rs_f8(const void* x, int64_t ldx, const void* w, int64_t ldw, float alpha, void* const* partial,
+                              const void* partial_multicast, int32_t* const* flags, void* output, int64_t ldo,
+                              int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
+                              int lagged_exit, gnk_stream_t stream) {
+  if (partial_multicast && !aligned16(partial_multicast)) return GNK_ERR_BAD_ARG;
+  return gemm_rs_impl(x, ldx, w, ldw, partial, partial_multicast, flags, output, ldo, M, N, K_local, rank, world,
+                      timeout_ms, lagged_exit, stream, nullptr, true, alpha);
 }

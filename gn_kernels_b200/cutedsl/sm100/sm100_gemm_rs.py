@@ -63,6 +63,7 @@ def gemm_rs(
     timeout_ms: int = 0,
     multicast: bool | None = None,
     lagged_exit: bool = False,
+    alpha: float | None = None,
 ) -> torch.Tensor:
     """output[M/W, N] = sum over ranks of bf16(x_r @ w_r^T)[this rank's rows], fp32 summation.
 
@@ -79,6 +80,8 @@ def gemm_rs(
     call on the same `flags` does that wait just before its first store, under its first tiles' math.
     `output` is complete either way; `partial` and `flags` then belong to the sequence until a call
     with `lagged_exit=False` ends it (or a host barrier across the ranks, then `flags.zero_()`).
+    float8_e4m3fn `x` and `w` (tensor-wise scaled; upstream's function is BF16 only) need `alpha`, this rank's
+    scale_x * scale_w: the rank's partial is then bf16(alpha * (x @ w^T)).
     BN is accepted for upstream
     compatibility; the tile shape is chosen from the problem shape."""
     assert dist.is_initialized()
@@ -87,7 +90,12 @@ def gemm_rs(
     assert world <= 8
     M, K = x.shape
     N, _ = w.shape
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and output.dtype == torch.bfloat16
+    fp8 = x.dtype == torch.float8_e4m3fn
+    assert (fp8 or x.dtype == torch.bfloat16) and w.dtype == x.dtype and output.dtype == torch.bfloat16
+    if fp8 and alpha is None:
+        raise ValueError("gemm_rs: float8_e4m3fn operands need alpha = scale_x * scale_w")
+    if fp8 and world == 1:
+        raise NotImplementedError("gemm_rs: float8_e4m3fn operands need at least 2 ranks (one rank: triton_mm with row scales)")
     assert w.shape[1] == K and output.shape == (M // world, N)
     assert x.stride(1) == 1 and w.stride(1) == 1 and output.stride(1) == 1
     stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
@@ -103,6 +111,17 @@ def gemm_rs(
             mc = p_mc
             if mc == 0 and multicast:
                 raise RuntimeError("gemm_rs: multicast=True but the symmetric-memory handle has no multicast address")
+    if fp8:
+        with torch.cuda.device(x.device):
+            check(
+                lib().gnk_gemm_rs_f8(
+                    ctypes.c_void_p(x.data_ptr()), x.stride(0), ctypes.c_void_p(w.data_ptr()), w.stride(0), float(alpha), sp,
+                    ctypes.c_void_p(mc) if mc else None, fp, ctypes.c_void_p(output.data_ptr()), output.stride(0), M, N, K,
+                    rank, world, timeout_ms, int(bool(lagged_exit)), stream,
+                ),
+                "gnk_gemm_rs_f8",
+            )
+        return output
     if mc:
         with torch.cuda.device(x.device):
             check(

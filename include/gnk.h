@@ -280,6 +280,16 @@ int gnk_gemm_rs_bf16_pull(const void* x, int64_t ldx, const void* w, int64_t ldw
                           int64_t M, int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms,
                           int lagged_exit, gnk_stream_t stream);
 
+/* The reduce-scatter for E4M3 operands with tensor-wise scales (no counterpart upstream, whose gemm_rs is
+ * BF16 only): x [M, K_local], w [N, K_local] float8_e4m3fn codes, alpha = scale_x * scale_w of this rank;
+ * partial_r = bf16(alpha * (x_r w_r^T)), summed over the ranks in fp32.  K_local % 16 == 0, world >= 2;
+ * partial_multicast NULL selects the push variant (partial[r] are then the staging buffers); everything
+ * else as for gnk_gemm_rs_bf16 / gnk_gemm_rs_bf16_pull. */
+int gnk_gemm_rs_f8(const void* x, int64_t ldx, const void* w, int64_t ldw, float alpha, void* const* partial,
+                   const void* partial_multicast, int32_t* const* flags, void* output, int64_t ldo, int64_t M,
+                   int64_t N, int64_t K_local, int rank, int world, uint32_t timeout_ms, int lagged_exit,
+                   gnk_stream_t stream);
+
 /* GEMM + all-reduce (no counterpart upstream, whose only fused collective is the reduce-scatter above): the
  * same kernel and buffers as gnk_gemm_rs_bf16_pull, but the owner of a block of rows stores each reduced
  * 16-byte piece through output_multicast, the NVLink multicast address of the ranks' [M, N] bf16 outputs

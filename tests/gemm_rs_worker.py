@@ -91,6 +91,35 @@ def main():
             dist.barrier()  # a faster peer's next call may signal this rank's flags as soon as it starts
         dist.barrier()
 
+        # E4M3 operands with tensor-wise scales: partial_r = bf16(alpha_r * (x_r w_r^T))
+        if Kl % 16 == 0:
+            sx, sw = x.abs().amax().float() / 448.0, w.abs().amax().float() / 448.0
+            x8, w8 = (x.float() / sx).to(torch.float8_e4m3fn), (w.float() / sw).to(torch.float8_e4m3fn)
+            a8 = float(sx) * float(sw)
+            x8s = [torch.empty_like(x8.view(torch.uint8)) for _ in range(W)]
+            w8s = [torch.empty_like(w8.view(torch.uint8)) for _ in range(W)]
+            a8s = [torch.empty(1, device=dev) for _ in range(W)]
+            dist.all_gather(x8s, x8.view(torch.uint8))
+            dist.all_gather(w8s, w8.view(torch.uint8))
+            dist.all_gather(a8s, torch.tensor([a8], device=dev))
+            refs8 = None
+            if rank == 0:
+                refs8 = ors.gemm_rs_f8([t.view(torch.float8_e4m3fn).cpu() for t in x8s], [t.view(torch.float8_e4m3fn).cpu() for t in w8s],
+                                       [float(t) for t in a8s])
+            o8 = torch.zeros_like(out)
+            gemm_rs(x8, w8, partial, ph, o8, flags, fh, alpha=a8)
+            torch.cuda.synchronize()
+            _lib.raise_on_device_error()
+            assert int(flags.abs().sum()) == 0, "flags not restored to zero after the fp8 reduce-scatter"
+            outs = [torch.empty_like(o8) for _ in range(W)]
+            dist.all_gather(outs, o8)
+            if rank == 0:
+                errs = [max_rel_err(o.cpu(), r) for o, r in zip(outs, refs8)]
+                ok = max(errs) <= 1e-2
+                print(f"gemm_rs fp8 W={W} M={M} N={N} K={Kl * W}: max rel err {max(errs):.2e} {'OK' if ok else 'FAIL'}", flush=True)
+                failures += 0 if ok else 1
+            dist.barrier()
+
         # GEMM + all-reduce (needs the multicast path): every rank ends with all rows of the sum
         if bool(getattr(ph, "multicast_ptr", 0)) and mcast is not False:
             full = symm_mem.empty(M, N, dtype=torch.bfloat16, device=dev)
