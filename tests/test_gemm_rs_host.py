@@ -127,3 +127,42 @@ def test_peer_addresses_apply_one_offset_to_every_mapping():
         peer_addresses(pool[8 : 8 + 4096].view(torch.bfloat16), h, 1, 3, 4096)
     flags = pool[4 : 4 + 64].view(torch.int32)
     assert peer_addresses(flags, h, 1, 3, 64, align=4)[0][1] == base + 4
+
+
+def test_oracle_variants_agree_with_the_reduce_scatter_statement():
+    """The all-reduce statement is the reduce-scatter outputs stacked, and the E4M3 statement with
+    alpha = 1 equals the bf16 statement on the same values (every E4M3 value is a bf16 value)."""
+    from oracle import gemm_rs as ors
+
+    g = torch.Generator().manual_seed(5)
+    W, M, N, Kl = 4, 16, 12, 32
+    xs = [torch.randn(M, Kl, generator=g).to(torch.float8_e4m3fn) for _ in range(W)]
+    ws = [torch.randn(N, Kl, generator=g).to(torch.float8_e4m3fn) for _ in range(W)]
+    rs = ors.gemm_rs([x.float().bfloat16() for x in xs], [w.float().bfloat16() for w in ws])
+    f8 = ors.gemm_rs_f8(xs, ws, [1.0] * W)
+    assert all(torch.equal(a, b) for a, b in zip(rs, f8))
+    ar = ors.gemm_ar([x.float().bfloat16() for x in xs], [w.float().bfloat16() for w in ws])
+    assert ar.shape == (M, N) and torch.equal(ar, torch.cat(rs, dim=0))
+    # a power-of-two factor moves every rank's partial exactly
+    f8s = ors.gemm_rs_f8(xs, ws, [0.25] * W)
+    assert all(torch.equal(a.float() * 0.25, b.float()) for a, b in zip(f8, f8s))
+
+
+def test_fp8_reduce_scatter_wrapper_refuses_missing_alpha():
+    """Argument checks that need no GPU work: E4M3 operands without `alpha` are refused before any launch."""
+    import torch.distributed as dist
+
+    from gn_kernels_b200.cutedsl.sm100.sm100_gemm_rs import gemm_rs
+
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29537", rank=0, world_size=1)
+    try:
+        x = torch.zeros(128, 64).to(torch.float8_e4m3fn)
+        w = torch.zeros(128, 64).to(torch.float8_e4m3fn)
+        out = torch.zeros(128, 128, dtype=torch.bfloat16)
+        with pytest.raises(ValueError):
+            gemm_rs(x, w, None, None, out, None, None)
+        with pytest.raises(NotImplementedError):
+            gemm_rs(x, w, None, None, out, None, None, alpha=1.0)
+    finally:
+        dist.destroy_process_group()
